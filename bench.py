@@ -1,0 +1,370 @@
+#!/usr/bin/env python3
+"""Benchmark of the logits sampling path: sampled rows/s at vocab 151 936.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the sampler over one batch of synthetic rows (the "throughput"
+workload: 4096 float32 rows x 151 936 columns per GPU, temperature 0.6, top-k 20,
+top-p 0.95, repeat penalty 1.1 over a 1024-id history).  Rows are independent, so with
+N GPUs every rank samples its own 4096 rows and there is no collective in the data path
+(weak scaling); `value` is the rows all ranks sampled divided by the slowest rank's time.
+
+Prints ONE JSON line on rank 0.  `value` is timed with the batch resident in HBM;
+`e2e` is the same metric through the host-buffer C-ABI call (pinned host inputs, copies
+inside the timed region); `roofline` relates the streaming kernel to measured HBM
+bandwidth; `cpu_baseline` is the CPU port of the reference sampler timed on this host.
+
+`--impl reference` times that CPU port alone, with every host thread, on the same
+workload (a bounded sample of rows per step) and prints the same kind of line.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+METRIC = "sampled rows/s at vocab 151936"
+UNIT = "rows/s"
+FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0
+
+# DRAM bytes one launch of the streaming kernel moves per algorithmic byte, from the ncu
+# capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the
+# algorithmic bytes of the captured launch).  None until a capture has been read.
+DRAM_TRAFFIC_RATIO = None
+
+
+def load_oracle():
+    """The CPU port of the reference sampler (oracle/): used here only as the timed CPU
+    baseline and as the checker of a few rows, never on the measured GPU path."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+
+    oracle_lib.lib()
+    return oracle_lib
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed
+    regions run (read-only queries)."""
+
+    REASONS = {
+        0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+        0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, device_index):
+        super().__init__(daemon=True)
+        self.samples = []
+        self.windows = []
+        self.stop_flag = False
+        self.ok = False
+        self.max_mhz = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(0.001)
+
+    def window(self, t0, t1):
+        self.windows.append((t0, t1))
+
+    def summary(self):
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "note": "NVML unavailable"}
+        inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in self.windows)]
+        if not inside:  # a region shorter than one sampling period: take the nearest samples
+            inside = self.samples[-3:]
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        reasons = [name for bit, name in self.REASONS.items() if mask & bit]
+        return {
+            "sm_mhz": statistics.median([s[1] for s in inside]) if inside else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": reasons,
+            "samples": len(inside),
+        }
+
+
+def dist_setup(gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+
+
+def max_over_ranks(x, world, device):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(fn, steps, world, device, clocks=None):
+    """Times exactly `steps` calls of fn with CUDA events on the launching stream, between
+    a barrier + synchronize on both sides; returns the slowest rank's milliseconds per step."""
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    barrier(world)
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize(device)
+    t1 = time.perf_counter()
+    barrier(world)
+    if clocks is not None:
+        clocks.window(t0, t1)
+    return max_over_ranks(start.elapsed_time(end) / steps, world, device)
+
+
+def cpu_baseline(O, w, seconds=6.0):
+    """Times the CPU port of the reference sampler on a bounded sample of the workload's
+    rows with every host thread (one sampler state per row, rows handed out dynamically)."""
+    cores = O.lib().mantle_oracle_max_threads()
+    logits = w.logits.cpu().numpy()
+    hist = None if w.history is None else w.history.cpu().numpy()
+    n_cal = min(w.rows, max(cores, 16))
+    t = time.perf_counter()
+    O.sample_rows(logits[:n_cal].copy(), w.params[:n_cal], history=None if hist is None else hist[:n_cal])
+    dt = time.perf_counter() - t
+    n = int(min(w.rows, max(n_cal, n_cal * seconds / max(dt, 1e-6))))
+    work = logits[:n].copy()
+    t = time.perf_counter()
+    out = O.sample_rows(work, w.params[:n], history=None if hist is None else hist[:n])
+    dt = time.perf_counter() - t
+    return {
+        "value": n / dt, "unit": UNIT, "cores": int(out["threads"]), "kind": "port",
+        "sample": "%d rows of the same workload, one pass, %.2f s" % (n, dt),
+    }, out["next"], n
+
+
+def run_reference(args):
+    """The reference arm: the CPU port of internal/logits/sampler.go on the host cores."""
+    world, rank, _ = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), 0
+    if rank != 0:
+        return
+    from mantle_b200 import workloads
+
+    O = load_oracle()
+    cores = O.lib().mantle_oracle_max_threads()
+    w = workloads.make(args.workload, rows=min(args.rows, 2048), device="cpu")
+    logits = w.logits.numpy()
+    hist = None if w.history is None else w.history.numpy()
+    # size a step at roughly one second of wall time
+    n_cal = min(w.rows, max(cores, 16))
+    t = time.perf_counter()
+    O.sample_rows(logits[:n_cal].copy(), w.params[:n_cal], history=None if hist is None else hist[:n_cal])
+    dt = time.perf_counter() - t
+    n = int(min(w.rows, max(n_cal, n_cal * 1.0 / max(dt, 1e-6))))
+    times = []
+    used = cores
+    for i in range(args.warmup + args.steps):
+        work = logits[:n].copy()
+        t = time.perf_counter()
+        out = O.sample_rows(work, w.params[:n], history=None if hist is None else hist[:n])
+        dt = time.perf_counter() - t
+        used = int(out["threads"])
+        if i >= args.warmup:
+            times.append(dt)
+    ms = 1e3 * sum(times) / len(times)
+    value = n / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "%s: %d rows x %d f32 columns per step (bounded sample of the 4096-row batch), "
+                               "history %d ids, temp 0.6 top_k 20 top_p 0.95 repeat_penalty 1.1"
+                               % (args.workload, n, w.vocab, 0 if hist is None else hist.shape[1]),
+                   "rows_per_step": n, "vocab": w.vocab},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": "port",
+                         "sample": "%d rows per step, %d steps" % (n, args.steps)},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "C port of the reference's Go sampler (no Go toolchain on this image), all host threads",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    from mantle_b200 import native, sampler, workloads
+
+    native.load()  # raises if the CUDA library is missing: there is no other path
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the sampler has no CPU path")
+    world, rank, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+
+    w = workloads.make(args.workload, rows=args.rows, device=device, seed=workloads.BASE_SEED + 3000 + rank)
+    p_dev = sampler.params_to_device(w.params, device)
+    plan = sampler.BatchPlan(w.logits, p_dev, w.max_top_k, history=w.history, want_counts=False, splits=args.splits)
+    step = plan.launch
+
+    clocks = ClockSampler(local)
+    clocks.start()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(device)
+    ms = time_steps(step, args.steps, world, device, clocks)
+    tokens = plan.out.next.cpu().numpy().copy()
+    status = int(plan.out.status.item())
+
+    # ---- end to end: pinned host buffers through the host-buffer C-ABI call -------------------
+    e2e = None
+    if not args.no_e2e:
+        host_logits = torch.empty(w.logits.shape, dtype=w.logits.dtype, pin_memory=True)
+        host_logits.copy_(w.logits)
+        host_hist = None
+        if w.history is not None:
+            host_hist = torch.empty(w.history.shape, dtype=torch.int32, pin_memory=True)
+            host_hist.copy_(w.history)
+        hplan = sampler.HostBatchPlan(host_logits, w.params, w.max_top_k, history=host_hist, device=device,
+                                      splits=args.splits)
+
+        def e2e_step():
+            hplan.launch()
+            torch.cuda.current_stream().synchronize()  # the caller reads the tokens after every step
+
+        for _ in range(3):
+            e2e_step()
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_ms = time_steps(e2e_step, e2e_steps, world, device, clocks)
+        assert np.array_equal(hplan.out.next.numpy(), tokens), "host-buffer path disagrees with the device path"
+        e2e = {
+            "value": w.rows * world / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms, "steps": e2e_steps,
+            "h2d_bytes_per_step": int(hplan.h2d_bytes), "d2h_bytes_per_step": int(hplan.d2h_bytes),
+        }
+        del hplan, host_logits
+
+    clocks.stop_flag = True
+    clocks.join(timeout=2)
+
+    # ---- CPU baseline and a parity spot check (rank 0, one GPU only) --------------------------------
+    cpu = None
+    parity_rows = 0
+    if rank == 0 and world == 1 and not args.no_cpu:
+        O = load_oracle()
+        cpu, cpu_tokens, n = cpu_baseline(O, w)
+        assert np.array_equal(cpu_tokens, tokens[:n]), "GPU tokens differ from the CPU port on the sampled rows"
+        parity_rows = n
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        rows_total = w.rows * world
+        kernel_bytes = w.rows * w.bytes_per_row  # one launch, one GPU
+        achieved = kernel_bytes / (ms / 1e3) / 1e9
+        line = {
+            "metric": METRIC, "value": rows_total / (ms / 1e3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": "%s: %d rows x %d f32 columns per GPU, history %d ids, temp 0.6 top_k 20 top_p 0.95 "
+                            "repeat_penalty 1.1, seeded N(0,3^2) logits with 16 boosted ids per row"
+                            % (args.workload, w.rows, w.vocab, 0 if w.history is None else w.history.shape[1]),
+                "rows_per_gpu": w.rows, "vocab": w.vocab, "parallelism": "rows sharded over %d GPU(s), no collective" % world,
+                "l2": "inputs (%.2f GB per GPU) exceed the 126 MB L2, no flush needed" % (kernel_bytes / 1e9),
+                "ctas_per_row": plan.splits,
+            },
+            "roofline": {
+                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None if DRAM_TRAFFIC_RATIO is None else DRAM_TRAFFIC_RATIO * kernel_bytes,
+                "peak_kind": "of %s" % peak_kind, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+                "kernel": "scan_rows_kernel<float, fused>", "algorithmic_bytes_per_launch": kernel_bytes,
+                "bytes_per_row": w.bytes_per_row,
+            },
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": args.steps * plan.kernels_per_launch,
+            "clocks": clocks.summary(),
+            "status_word": status,
+            "parity_rows_checked": parity_rows,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="throughput")
+    ap.add_argument("--rows", type=int, default=4096, help="rows per GPU")
+    ap.add_argument("--splits", type=int, default=0, help="CTAs per row (0: library's choice)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,186 @@
+/*
+ * C-ABI of the device-side logits sampler (sm_100a).
+ *
+ * These are the symbols a cgo file under internal/backend/cuda/native binds, next to
+ * the reference's own wrappers.  They follow that package's conventions
+ * (internal/backend/cuda/native/softmax.h:1-115, softmax.cu:972-988, 1151-1160):
+ * `extern "C" int mantleCudaXxx(..., cudaStream_t stream)` returning a cudaError_t as
+ * int, 0 on success, cudaErrorInvalidValue (1) for bad arguments; work is queued on
+ * `stream` and the call returns without synchronising.  Unlike the reference's
+ * ArgMaxF32 (native/argmax.go:32-53) nothing here allocates, frees or copies to the
+ * host behind the caller's back: every buffer, the workspace included, is the caller's.
+ * The current device must be the one that owns the buffers.
+ *
+ * What the kernels compute is Sampler.Sample of internal/logits/sampler.go:98-234 for
+ * every row of a batch: repeat penalty over the de-duplicated history window, the
+ * greedy test and lowest-index argmax, temperature scaling, the top-k shortlist
+ * (value descending, ties by ascending index), fastExp softmax over the shortlist in
+ * float32 with double sums, min-p, the top-p cut and the inverse-CDF draw from a
+ * host-supplied uniform.  Token ids equal the reference's on the same inputs.
+ */
+#ifndef MANTLE_CUDA_SAMPLER_H
+#define MANTLE_CUDA_SAMPLER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "mantle_sample_params.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef MANTLE_CUDA_STREAM_T
+#define MANTLE_CUDA_STREAM_T
+typedef void* mantleCudaStream_t; /* a cudaStream_t, as in native/softmax.h:11 */
+#endif
+
+#define MANTLE_DTYPE_F32 0
+#define MANTLE_DTYPE_BF16 1
+
+/* Largest top_k the shortlist kernels take.  The reference's shortlist loop is
+ * O(V*k) and meant for small k (sampler.go:252-254); its default is 40. */
+#define MANTLE_SAMPLE_MAX_TOP_K 1024
+/* Largest vocabulary (per GPU) the kernels take: the penalty bitmap of V bits lives
+ * in shared memory beside the candidate buffer. */
+#define MANTLE_SAMPLE_MAX_VOCAB 1048576
+
+/* flags */
+/* Store the penalised logits back, as the reference does to the caller's slice
+ * (sampler.go:132-136).  Without it the logits are read-only and the penalty is
+ * applied on the fly while the row streams past.  float32 logits only. */
+#define MANTLE_SAMPLE_WRITE_BACK_PENALTY 1u
+/* The history is ignored: mantleCudaRepeatPenaltyRowsF32 already ran on these logits. */
+#define MANTLE_SAMPLE_PENALTY_PREAPPLIED 2u
+
+/* bits of the optional device status word (OR-ed in by the kernels; never cleared) */
+#define MANTLE_SAMPLE_STATUS_TOPK_RANGE 1  /* a row's top_k exceeded max_top_k          */
+#define MANTLE_SAMPLE_STATUS_EMPTY 2       /* a row ended with an empty shortlist (the  */
+                                           /* reference panics there); its token is -1  */
+
+/*
+ * One batch of rows.  All pointers are device pointers on the current device.
+ *
+ *   logits      [rows][row_stride] elements of `dtype`; row r starts at r*row_stride;
+ *               only the first `vocab` elements of a row are read
+ *   history     [rows][hist_stride] int32 token ids, oldest first (the reference's
+ *               `recent`); may be NULL (no penalty).  hist_len[r] <= hist_stride ids are
+ *               valid; NULL means hist_stride for every row.  The window is the last
+ *               params[r].repeat_last_n of them (sampler.go:100-101)
+ *   exclude     n_exclude ids never penalised (the reference's excludePenalty: the stop
+ *               tokens, engine.go:233); one list for the batch; may be NULL
+ *   params      [rows] normalised per-row parameters
+ *   next        [rows] out: the sampled token id of each row
+ *   cand_idx, cand_prob  optional out, [rows][cand_stride]: the shortlist after min-p,
+ *               in order, and its probabilities (double, as the reference holds them);
+ *               at most cand_stride entries per row are written
+ *   n_kept, cut optional out, [rows]: shortlist length after min-p and nucleus length
+ *               after top-p; both 0 on greedy rows
+ *   status      optional out: one int32 the kernels OR status bits into
+ *   max_top_k   an upper bound of params[r].top_k over the batch,
+ *               1..MANTLE_SAMPLE_MAX_TOP_K; sizes the workspace
+ *   splits      CTAs per row: 0 lets the library choose (1 for batches that fill the
+ *               GPU, more for small batches); > 1 needs the workspace
+ */
+typedef struct MantleSampleBatch {
+    const void* logits;
+    int32_t dtype;
+    int32_t rows;
+    int32_t vocab;
+    int32_t max_top_k;
+    int64_t row_stride;
+    const int32_t* history;
+    const int32_t* hist_len;
+    int32_t hist_stride;
+    int32_t n_exclude;
+    const int32_t* exclude;
+    const MantleSampleParams* params;
+    int32_t* next;
+    int32_t* cand_idx;
+    double* cand_prob;
+    int32_t* n_kept;
+    int32_t* cut;
+    int32_t* status;
+    int32_t cand_stride;
+    int32_t splits;
+    uint32_t flags;
+    uint32_t reserved;
+} MantleSampleBatch;
+
+/*
+ * Sampler.Sample for every row (replaces internal/logits/sampler.go:98-234, called from
+ * internal/inference/engine.go:233,279,296).  `workspace` may be NULL when the batch
+ * runs with one CTA per row; mantleCudaSamplerWorkspaceBytes says how much a batch needs.
+ */
+int mantleCudaSampleRows(const MantleSampleBatch* batch, void* workspace, size_t workspace_bytes,
+                         mantleCudaStream_t stream);
+
+/* Bytes of workspace mantleCudaSampleRows needs for this batch (0 when none). */
+int mantleCudaSamplerWorkspaceBytes(const MantleSampleBatch* batch, size_t* bytes);
+
+/* The number of CTAs per row mantleCudaSampleRows will use for this batch. */
+int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* splits);
+
+/*
+ * The repeat penalty alone, in place, one scatter over the de-duplicated history
+ * window of each row (sampler.go:99-138).  Takes the same descriptor; reads logits
+ * (float32), history, hist_len, exclude and params and writes only logits.
+ */
+int mantleCudaRepeatPenaltyRowsF32(const MantleSampleBatch* batch, mantleCudaStream_t stream);
+
+/*
+ * Index of the maximum of each row, the lowest index on ties (argmax,
+ * sampler.go:237-250).  Batched replacement for mantleCudaArgMaxF32
+ * (native/softmax.cu:663-704,1151-1160), whose tie-break follows thread order.
+ */
+int mantleCudaArgMaxRowsF32(const float* x, int rows, int n, int64_t row_stride, int* out_idx,
+                            mantleCudaStream_t stream);
+
+/*
+ * Vocabulary-sharded sampling, step 1: this GPU holds columns
+ * [vocab_offset, vocab_offset + batch->vocab) of a vocab_total-wide row.  Applies the
+ * penalty to the ids it owns, scales, and writes its local shortlist: for row r,
+ * part_cnt[r] <= part_cap entries at part_val/part_idx[r*part_cap ...], value descending,
+ * part_idx holding GLOBAL token ids.  history/exclude hold global ids.
+ */
+int mantleCudaSampleLocalTopK(const MantleSampleBatch* batch, int vocab_offset, int vocab_total,
+                              float* part_val, int32_t* part_idx, int32_t* part_cnt, int part_cap,
+                              mantleCudaStream_t stream);
+
+/*
+ * Vocabulary-sharded sampling, step 2 (after the caller's all-gather): merges `parts`
+ * shortlists per row -- part p of row r at [(p*rows + r)*part_cap ...], its length at
+ * part_cnt[p*rows + r] -- into the global shortlist and finishes the row (softmax,
+ * min-p, top-p, draw).  Uses params, next and the optional outputs of `batch`;
+ * parts * max_top_k must not exceed 4096.
+ */
+int mantleCudaSampleMergeParts(const MantleSampleBatch* batch, int parts, const float* part_val,
+                               const int32_t* part_idx, const int32_t* part_cnt, int part_cap,
+                               mantleCudaStream_t stream);
+
+/*
+ * Sampler.Sample for a batch that lives in HOST memory: the form of the reference's
+ * call site, where the logits arrive as a host slice (internal/inference/engine.go:233,
+ * 279, 296 pass `logitsVec []float32`).  Every pointer of `host_batch` (logits, history,
+ * hist_len, exclude, params and all outputs) is a host pointer, pinned for the copies to
+ * be asynchronous.  The call queues, on `stream`: the host-to-device copies of the inputs
+ * into `device_workspace`, the same kernels as mantleCudaSampleRows, and the
+ * device-to-host copies of next and of every optional output that is set.  With
+ * MANTLE_SAMPLE_WRITE_BACK_PENALTY the penalised logits are copied back over the host
+ * rows too, which is the reference's in-place side effect (sampler.go:132-136).
+ * The caller synchronises `stream` before reading the outputs.
+ */
+int mantleCudaSampleRowsHost(const MantleSampleBatch* host_batch, void* device_workspace,
+                             size_t workspace_bytes, mantleCudaStream_t stream);
+
+/* Bytes of device workspace mantleCudaSampleRowsHost needs for this batch. */
+int mantleCudaSamplerHostWorkspaceBytes(const MantleSampleBatch* host_batch, size_t* bytes);
+
+/* Library version, for the loader's sanity check. */
+int mantleCudaSamplerAbiVersion(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MANTLE_CUDA_SAMPLER_H */

@@ -1,0 +1,76 @@
+"""Shared helpers of the GPU parity tests: run a batch through the CUDA C-ABI and through
+the CPU oracle on identical bytes and compare everything the two report."""
+import numpy as np
+import torch
+
+import oracle_lib as O
+from mantle_b200 import native, sampler
+
+
+def to_bf16_bits(t):
+    """bfloat16 torch tensor -> numpy uint16 bit patterns."""
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def run_gpu(logits, params, max_top_k, history=None, hist_len=None, exclude=None, cand_cap=0, flags=0, splits=0,
+            vocab=None):
+    """logits: CUDA tensor.  Returns dict of numpy arrays plus the plan."""
+    dev = logits.device
+    p_dev = sampler.params_to_device(params, dev)
+    h_dev = None if history is None else torch.as_tensor(np.ascontiguousarray(history, dtype=np.int32)).to(dev)
+    hl_dev = None if hist_len is None else torch.as_tensor(np.ascontiguousarray(hist_len, dtype=np.int32)).to(dev)
+    ex_dev = None if exclude is None else torch.as_tensor(np.ascontiguousarray(exclude, dtype=np.int32)).to(dev)
+    with torch.cuda.device(dev):
+        plan = sampler.BatchPlan(logits, p_dev, max_top_k, history=h_dev, hist_len=hl_dev, exclude=ex_dev,
+                                 cand_cap=cand_cap, flags=flags, splits=splits, vocab=vocab)
+        out = plan.launch()
+        torch.cuda.synchronize(dev)
+    res = dict(
+        next=out.next.cpu().numpy(),
+        n_kept=out.n_kept.cpu().numpy(),
+        cut=out.cut.cpu().numpy(),
+        status=int(out.status.item()),
+        cand_idx=None if out.cand_idx is None else out.cand_idx.cpu().numpy(),
+        cand_prob=None if out.cand_prob is None else out.cand_prob.cpu().numpy(),
+        splits=plan.splits,
+    )
+    return res
+
+
+def compare(gpu, ref, cand_cap=0, exact_prob=True, where=""):
+    """Token ids, shortlist lengths, nucleus lengths and shortlist ids are integers: exact.
+    Probabilities: bit-equal doubles where both sides sum in shortlist order; always within
+    1e-5 relative after rounding to float32 (the tolerance the sampling contract states)."""
+    assert np.array_equal(gpu["next"], ref["next"]), (where, np.nonzero(gpu["next"] != ref["next"])[0][:8],
+                                                      gpu["next"][:8], ref["next"][:8])
+    assert np.array_equal(gpu["n_kept"], ref["n_kept"]), where
+    assert np.array_equal(gpu["cut"], ref["cut"]), where
+    if cand_cap:
+        rows = len(ref["next"])
+        for r in range(rows):
+            n = min(int(ref["n_kept"][r]), cand_cap)
+            assert np.array_equal(gpu["cand_idx"][r, :n], ref["cand_idx"][r, :n]), (where, r)
+            a, b = gpu["cand_prob"][r, :n], ref["cand_prob"][r, :n]
+            if exact_prob:
+                assert np.array_equal(a, b), (where, r)
+            a32, b32 = a.astype(np.float32), b.astype(np.float32)
+            assert np.all(np.abs(a32 - b32) <= 1e-5 * np.abs(b32)), (where, r)
+
+
+def check_against_oracle(logits_np, params, max_top_k, history=None, hist_len=None, exclude=None, cand_cap=0,
+                         flags=0, splits=0, device="cuda:0", where="", bf16=False):
+    """logits_np: float32 [rows, V] host array (or uint16 bf16 bits when bf16=True)."""
+    if bf16:
+        dev_logits = torch.from_numpy(logits_np.view(np.int16).copy()).to(device).view(torch.bfloat16)
+    else:
+        dev_logits = torch.from_numpy(logits_np.copy()).to(device)
+    gpu = run_gpu(dev_logits, params, max_top_k, history, hist_len, exclude, cand_cap, flags, splits)
+    ref_logits = logits_np.copy()
+    ref = O.sample_rows(ref_logits, params, history=history, hist_len=hist_len, exclude=exclude, cand_cap=cand_cap)
+    compare(gpu, ref, cand_cap, where=where)
+    assert gpu["status"] == 0, where
+    if flags & native.FLAG_WRITE_BACK_PENALTY:
+        assert np.array_equal(dev_logits.cpu().numpy(), ref_logits), where  # the in-place side effect
+    elif not bf16:
+        assert np.array_equal(dev_logits.cpu().numpy(), logits_np), where   # read-only otherwise
+    return gpu, ref

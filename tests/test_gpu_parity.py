@@ -1,0 +1,340 @@
+"""Parity of the CUDA sampler with the CPU oracle, through the C-ABI, on a B200."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as O
+from gpu_util import check_against_oracle, compare, run_gpu, to_bf16_bits
+from mantle_b200 import native, sampler, workloads
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def P(uniform=0.5, **cfg):
+    return O.normalize(uniform=uniform, **cfg)
+
+
+def one(logits, uniform=0.5, recent=None, exclude=None, cand_cap=8, flags=0, **cfg):
+    p = np.array([P(uniform, **cfg)])
+    lg = np.array([logits], dtype=np.float32)
+    hist = None if recent is None else np.array([recent], dtype=np.int32)
+    return check_against_oracle(lg, p, max(1, min(int(p[0]["top_k"]), 1024)), history=hist, exclude=exclude,
+                                cand_cap=cand_cap, flags=flags)
+
+
+# ---- the reference's own test vectors (internal/logits/sampler_test.go) through the C-ABI --------
+
+def test_reference_vectors():
+    g, _ = one([-1, 5, 3, 7, 2], seed=99, temperature=1.0, top_k=1, top_p=1.0)  # :20-27
+    assert g["next"][0] == 3
+    g, _ = one([-1, 5, 3, 7, 2], seed=99, temperature=0.0, top_k=40, top_p=0.95)  # :29-41
+    assert g["next"][0] == 3
+    for r in [0.0, 0.3, 0.999999, 1.0 - 2.0 ** -53]:  # :47-58
+        g, _ = one([10, 0, 0, 0, 0], uniform=r, seed=7, temperature=1.0, top_k=5, top_p=0.5)
+        assert g["next"][0] == 0 and g["cut"][0] == 1
+    a, _ = one([0, 1, 2, 3, 4, 5], uniform=0.37, seed=42, temperature=0.9, top_k=4, top_p=0.95)  # :7-16
+    b, _ = one([0, 1, 2, 3, 4, 5], uniform=0.37, seed=42, temperature=0.9, top_k=4, top_p=0.95)
+    assert a["next"][0] == b["next"][0]
+    g, _ = one([1, 0], temperature=0.0)  # inference/engine_panic_test.go:29-35
+    assert g["next"][0] == 0
+
+
+# ---- hand-derived branch cases ---------------------------------------------------------------------
+
+def test_penalty_rules():
+    for flags in (0, native.FLAG_WRITE_BACK_PENALTY):
+        g, _ = one([2.0, -2.0, 0.0, 4.0, 1.0, 3.0], recent=[0, 1, 0, 2, 5, 99, -1], exclude=[5], temperature=0.0,
+                   repeat_penalty=2.0, repeat_last_n=64, flags=flags)
+        assert g["next"][0] == 3
+        g, _ = one([5.0, 4.0, 3.0], recent=[0, 1, 2], temperature=0.0, repeat_penalty=2.0, repeat_last_n=2, flags=flags)
+        assert g["next"][0] == 0
+        g, _ = one([5.0, 4.9], recent=[0], temperature=0.0, repeat_penalty=1.1, flags=flags)
+        assert g["next"][0] == 1
+        one([5.0, 4.0, 3.0], recent=[0, 1, 2], temperature=0.7, top_k=3, repeat_penalty=0.5, flags=flags)
+        one([5.0, 4.0, 3.0], recent=[0, 1, 2], temperature=0.7, top_k=3, repeat_penalty=1.0, flags=flags)
+
+
+def test_ties_and_signed_zero():
+    g, _ = one([1.0, 7.0, 7.0, -0.0, 7.0], temperature=0.0)
+    assert g["next"][0] == 1
+    g, _ = one([-0.0, 0.0, -1.0], temperature=0.0)
+    assert g["next"][0] == 0
+    g, _ = one([0.0, -0.0, 0.0, -5.0], uniform=0.5, temperature=1.0, top_k=2, top_p=1.0)
+    assert g["cand_idx"][0, :2].tolist() == [0, 1]
+    g, _ = one([1, 3, 3, 2, 3, 0], uniform=0.9, temperature=1.0, top_k=2, top_p=1.0)
+    assert g["cand_idx"][0, :2].tolist() == [1, 2]
+
+
+def test_tail_branches():
+    g, _ = one([1.0, 2.0, 0.5], uniform=0.99, temperature=0.5, top_k=1, top_p=1.0)
+    assert g["next"][0] == 1 and g["n_kept"][0] == 1
+    g, _ = one([0.0, 0.0, 0.0, 0.0], uniform=1.0 - 2.0 ** -53, temperature=1.0, top_k=4, top_p=1.0)
+    assert g["cut"][0] == 4 and g["next"][0] == 3
+    g, _ = one([0.0, 0.0, 0.0, 0.0], uniform=0.9, temperature=1.0, top_k=4, top_p=0.5)
+    assert g["cut"][0] == 2 and g["next"][0] == 1
+    g, _ = one([4.0, 3.9, 0.0, -3.0], uniform=0.999, temperature=1.0, top_k=4, top_p=1.0, min_p=0.5)
+    assert g["n_kept"][0] == 2 and g["next"][0] == 1
+    g, _ = one([0.5, 1.5], uniform=0.0, temperature=1.0, top_k=40, top_p=1.0)
+    assert g["n_kept"][0] == 2 and g["next"][0] == 1
+    one([100.0, -100.0, 0.0], uniform=0.5, temperature=0.3, top_k=3, top_p=0.9)  # fast_exp below -88
+
+
+# ---- seeded random small cases, every parameter combination -----------------------------------------
+
+def random_params(rng, rows, ks=(0, 1, 2, 5, 40, 300)):
+    params = np.zeros(rows, dtype=O.PARAMS_DTYPE)
+    for r in range(rows):
+        params[r] = O.normalize(
+            temperature=float(rng.choice([0.0, 0.3, 0.8, 1.0, 1.5])),
+            top_k=int(rng.choice(ks)),
+            top_p=float(rng.choice([0.0, 0.5, 0.9, 0.95, 1.0])),
+            min_p=float(rng.choice([0.0, 0.05, 0.3])),
+            repeat_penalty=float(rng.choice([0.0, 1.0, 1.1, 1.3])),
+            repeat_last_n=int(rng.choice([0, 4, 64])),
+            uniform=float(rng.random()),
+        )
+    return params
+
+
+@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("flags", [0, native.FLAG_WRITE_BACK_PENALTY])
+def test_random_small(seed, flags):
+    rng = np.random.default_rng(500 + seed)
+    rows = 48
+    V = int(rng.choice([1, 2, 3, 7, 33, 64, 257, 1000, 5000, 9001]))
+    logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    if seed % 2:
+        logits = (np.round(logits * 2) / 2).astype(np.float32)  # heavy ties
+    logits[rng.random((rows, V)) < 0.05] = 0.0
+    logits[rng.random((rows, V)) < 0.02] = -0.0
+    H = 40
+    hist = rng.integers(-2, V + 2, size=(rows, H)).astype(np.int32)
+    hist_len = rng.integers(0, H + 1, size=rows).astype(np.int32)
+    exclude = rng.integers(0, V, size=3).astype(np.int32)
+    params = random_params(rng, rows)
+    check_against_oracle(logits, params, 300, history=hist, hist_len=hist_len, exclude=exclude, cand_cap=min(V, 300),
+                         flags=flags, where="seed %d V %d" % (seed, V))
+
+
+@pytest.mark.parametrize("V", [4096 * 2 + 5, 40000, 151936])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_random_wide(V, splits):
+    rng = np.random.default_rng(V + splits)
+    rows = 24
+    logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    hist = rng.integers(0, V, size=(rows, 300)).astype(np.int32)
+    params = random_params(rng, rows, ks=(0, 1, 20, 50, 200, 512))
+    g, _ = check_against_oracle(logits, params, 512, history=hist, cand_cap=512, splits=splits,
+                                where="V %d splits %d" % (V, splits))
+    assert g["splits"] == splits
+
+
+def test_unaligned_rows_and_stride():
+    # rows that start off a 16-byte boundary: odd vocabulary with a dense layout, and a padded stride
+    rng = np.random.default_rng(77)
+    for V, stride in [(9999, 9999), (10001, 10003), (151937, 151937)]:
+        rows = 9
+        full = (rng.standard_normal((rows, stride)) * 3).astype(np.float32)
+        full[:, V:] = 1e30  # padding beyond the vocabulary must never be read as a candidate
+        params = random_params(rng, rows, ks=(1, 20, 200))
+        hist = rng.integers(0, V, size=(rows, 64)).astype(np.int32)
+        dev = torch.from_numpy(full).to(DEV)
+        gpu = run_gpu(dev, params, 200, history=hist, cand_cap=200, vocab=V)
+        ref = O.sample_rows(np.ascontiguousarray(full[:, :V]), params, history=hist, cand_cap=200)
+        compare(gpu, ref, 200, where="V %d stride %d" % (V, stride))
+
+
+def test_bf16_rows():
+    rng = np.random.default_rng(5)
+    rows, V = 16, 128256
+    t = (torch.from_numpy(rng.standard_normal((rows, V)).astype(np.float32)) * 2).to(torch.bfloat16)
+    bits = to_bf16_bits(t)
+    params = random_params(rng, rows, ks=(1, 20, 50, 400))
+    hist = rng.integers(0, V, size=(rows, 128)).astype(np.int32)
+    check_against_oracle(bits, params, 400, history=hist, cand_cap=400, bf16=True)
+    check_against_oracle(bits[:, :1001].copy(), params, 400, history=hist, cand_cap=400, bf16=True, splits=1)
+
+
+# ---- inputs built to break a streaming selection -----------------------------------------------------
+
+@pytest.mark.parametrize("kind", ["ascending", "descending", "all_equal", "mostly_neg_inf", "two_values", "huge_k"])
+def test_adversarial_rows(kind):
+    rng = np.random.default_rng(11)
+    rows, V = 6, 60000
+    if kind == "ascending":
+        logits = np.tile(np.linspace(-20, 20, V, dtype=np.float32), (rows, 1))
+    elif kind == "descending":
+        logits = np.tile(np.linspace(20, -20, V, dtype=np.float32), (rows, 1))
+    elif kind == "all_equal":
+        logits = np.full((rows, V), 1.25, dtype=np.float32)
+    elif kind == "mostly_neg_inf":
+        logits = np.full((rows, V), -np.inf, dtype=np.float32)
+        for r in range(rows):
+            logits[r, rng.integers(0, V, size=7)] = rng.standard_normal(7).astype(np.float32)
+    elif kind == "two_values":
+        logits = rng.choice(np.array([0.5, 2.0], dtype=np.float32), size=(rows, V))
+    else:
+        logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    ks = (600, 1024) if kind == "huge_k" else (1, 20, 200)
+    params = random_params(rng, rows, ks=ks)
+    hist = rng.integers(0, V, size=(rows, 64)).astype(np.int32)
+    for splits in (1, 2):
+        check_against_oracle(logits, params, 1024 if kind == "huge_k" else 200, history=hist,
+                             cand_cap=1024 if kind == "huge_k" else 200, splits=splits, where=kind)
+
+
+# ---- the benchmark configurations ---------------------------------------------------------------------
+
+def test_config_single_row():
+    w = workloads.make("single_row", device=DEV)
+    check_against_oracle(w.logits.cpu().numpy(), w.params, w.max_top_k, history=w.history.cpu().numpy(), cand_cap=20)
+
+
+def test_config_mixed_batch():
+    w = workloads.make("mixed_batch", device=DEV)
+    assert set(np.unique(w.params["top_k"])) <= {1, 20, 40, 50, 200}  # 0 became 40
+    for splits in (0, 1):
+        check_against_oracle(w.logits.cpu().numpy(), w.params, w.max_top_k, history=w.history.cpu().numpy(),
+                             cand_cap=200, splits=splits)
+
+
+def test_config_throughput_slice():
+    w = workloads.make("throughput", rows=512, device=DEV)
+    g, _ = check_against_oracle(w.logits.cpu().numpy(), w.params, w.max_top_k, history=w.history.cpu().numpy(),
+                                cand_cap=20)
+    assert g["splits"] == 1
+
+
+def test_full_size_properties():
+    """4096 x 151936: too large for the oracle in seconds, so size-independent properties:
+    the launch is idempotent (logits are read-only), every token lies in its row's top-20 of
+    penalised logits as torch orders them, permuting the rows permutes the tokens, and a
+    greedy pass over the same rows equals torch's argmax where the maximum is unique."""
+    w = workloads.make("throughput", device=DEV)
+    rows = w.rows
+    a = run_gpu(w.logits, w.params, w.max_top_k, history=w.history.cpu().numpy(), cand_cap=20)
+    b = run_gpu(w.logits, w.params, w.max_top_k, history=w.history.cpu().numpy(), cand_cap=20)
+    for key in ("next", "n_kept", "cut", "cand_idx", "cand_prob"):
+        assert np.array_equal(a[key], b[key])
+    assert a["status"] == 0 and np.all(a["n_kept"] == 20) and np.all(a["cut"] >= 1)
+    # oracle on a strided sample of the full batch
+    sel = np.arange(0, rows, 61)
+    ref = O.sample_rows(w.logits[sel].cpu().numpy(), w.params[sel], history=w.history[sel].cpu().numpy(), cand_cap=20)
+    sub = {k: (v[sel] if isinstance(v, np.ndarray) else v) for k, v in a.items()}
+    compare(sub, ref, 20)
+    # row permutation
+    perm = torch.randperm(rows, generator=torch.Generator().manual_seed(3))
+    c = run_gpu(w.logits[perm.to(DEV)].contiguous(), w.params[perm.numpy()], w.max_top_k,
+                history=w.history.cpu().numpy()[perm.numpy()], cand_cap=0)
+    assert np.array_equal(c["next"], a["next"][perm.numpy()])
+    # greedy == torch argmax (no penalty)
+    g = sampler.argmax_rows(w.logits).cpu().numpy()
+    assert np.array_equal(g, torch.argmax(w.logits, dim=1).cpu().numpy())
+    # the token is one of the shortlist ids, inside the nucleus
+    pos = (a["cand_idx"] == a["next"][:, None]).argmax(axis=1)
+    assert np.all(a["cand_idx"][np.arange(rows), pos] == a["next"]) and np.all(pos < a["cut"])
+
+
+# ---- stand-alone entry points ---------------------------------------------------------------------------
+
+def test_argmax_rows():
+    rng = np.random.default_rng(2)
+    for rows, V in [(1, 1), (3, 5), (7, 4097), (300, 151936), (5, 200001)]:
+        x = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+        x = (np.round(x * 4) / 4).astype(np.float32)
+        want = np.array([O.lib().mantle_oracle_argmax(x[r].ctypes.data_as(C.c_void_p), V) for r in range(rows)])
+        got = sampler.argmax_rows(torch.from_numpy(x).to(DEV)).cpu().numpy()
+        assert np.array_equal(got, want), (rows, V)
+    x = np.array([[-0.0, 0.0, -1.0], [1.0, 7.0, 7.0]], dtype=np.float32)
+    assert sampler.argmax_rows(torch.from_numpy(x).to(DEV)).cpu().numpy().tolist() == [0, 1]
+
+
+def test_repeat_penalty_rows_in_place_then_preapplied():
+    rng = np.random.default_rng(3)
+    rows, V = 20, 30000
+    logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    hist = rng.integers(-3, V + 3, size=(rows, 500)).astype(np.int32)
+    hist_len = rng.integers(0, 501, size=rows).astype(np.int32)
+    exclude = hist[:, 0].copy()[:5]
+    params = random_params(rng, rows, ks=(1, 20, 50))
+    dev = torch.from_numpy(logits.copy()).to(DEV)
+    p_dev = sampler.params_to_device(params, DEV)
+    sampler.repeat_penalty_rows_(dev, p_dev, torch.from_numpy(hist).to(DEV), torch.from_numpy(hist_len).to(DEV),
+                                 torch.from_numpy(exclude).to(DEV))
+    ref_logits = logits.copy()
+    ref = O.sample_rows(ref_logits, params, history=hist, hist_len=hist_len, exclude=exclude, cand_cap=50)
+    assert np.array_equal(dev.cpu().numpy(), ref_logits)
+    gpu = run_gpu(dev, params, 50, history=hist, hist_len=hist_len, exclude=exclude, cand_cap=50,
+                  flags=native.FLAG_PENALTY_PREAPPLIED)
+    compare(gpu, ref, 50)
+
+
+def test_vocab_sharded_on_one_gpu():
+    """Eight column shards of one row set, each run as its own local top-k, then merged:
+    equal to the oracle on the whole row (the all-gather is the caller's and moves bytes only)."""
+    w = workloads.make("vocab_sharded", rows=64, device=DEV)
+    V, G = w.vocab, 8
+    p_dev = sampler.params_to_device(w.params, DEV)
+    vals, idxs, cnts = [], [], []
+    for g in range(G):
+        lo = g * (V // G)
+        shard = w.logits[:, lo:lo + V // G].contiguous()
+        v, i, c = sampler.local_topk(shard, p_dev, w.max_top_k, lo, V, history=w.history)
+        vals.append(v), idxs.append(i), cnts.append(c)
+    out = sampler.merge_parts(p_dev, w.max_top_k, V, torch.stack(vals), torch.stack(idxs), torch.stack(cnts),
+                              cand_cap=50)
+    torch.cuda.synchronize()
+    gpu = dict(next=out.next.cpu().numpy(), n_kept=out.n_kept.cpu().numpy(), cut=out.cut.cpu().numpy(),
+               cand_idx=out.cand_idx.cpu().numpy(), cand_prob=out.cand_prob.cpu().numpy())
+    ref = O.sample_rows(w.logits.cpu().numpy(), w.params, history=w.history.cpu().numpy(), cand_cap=50)
+    compare(gpu, ref, 50)
+
+
+# ---- errors -------------------------------------------------------------------------------------------------
+
+def test_top_k_beyond_bound_sets_status():
+    params = np.array([P(0.5, temperature=1.0, top_k=50, top_p=1.0), P(0.5, temperature=1.0, top_k=5, top_p=1.0)])
+    logits = torch.randn(2, 1000, device=DEV)
+    g = run_gpu(logits, params, 10, cand_cap=10)
+    assert g["status"] & native.STATUS_TOPK_RANGE
+    assert g["next"][0] == -1 and 0 <= g["next"][1] < 1000
+
+
+def test_outputs_do_not_overrun():
+    rng = np.random.default_rng(8)
+    rows, V = 5, 3000
+    logits = torch.from_numpy((rng.standard_normal((rows, V)) * 3).astype(np.float32)).to(DEV)
+    params = np.array([P(float(rng.random()), temperature=0.9, top_k=40, top_p=1.0) for _ in range(rows)])
+    g = run_gpu(logits, params, 40, cand_cap=8)  # fewer candidate slots than the shortlist: truncated, not overrun
+    ref = O.sample_rows(logits.cpu().numpy(), params, cand_cap=8)
+    assert np.array_equal(g["next"], ref["next"]) and np.array_equal(g["cand_idx"], ref["cand_idx"])
+
+
+def test_host_buffer_entry_point():
+    """The host-slice form: pinned host inputs in, token ids out, copies inside the call."""
+    rng = np.random.default_rng(21)
+    rows, V = 40, 50000
+    logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    hist = rng.integers(0, V, size=(rows, 100)).astype(np.int32)
+    hist_len = rng.integers(0, 101, size=rows).astype(np.int32)
+    exclude = np.array([hist[0, 0], 7], dtype=np.int32)
+    params = random_params(rng, rows, ks=(1, 20, 50))
+    for flags in (0, native.FLAG_WRITE_BACK_PENALTY):
+        for splits in (0, 1):
+            host_logits = torch.from_numpy(logits.copy())
+            plan = sampler.HostBatchPlan(host_logits, params, 50, history=torch.from_numpy(hist),
+                                         hist_len=torch.from_numpy(hist_len), exclude=torch.from_numpy(exclude),
+                                         cand_cap=50, flags=flags, splits=splits, device=DEV)
+            out = plan.launch()
+            torch.cuda.synchronize()
+            ref_logits = logits.copy()
+            ref = O.sample_rows(ref_logits, params, history=hist, hist_len=hist_len, exclude=exclude, cand_cap=50)
+            gpu = dict(next=out.next.numpy(), n_kept=out.n_kept.numpy(), cut=out.cut.numpy(),
+                       cand_idx=out.cand_idx.numpy(), cand_prob=out.cand_prob.numpy())
+            compare(gpu, ref, 50)
+            assert int(out.status.item()) == 0
+            want = ref_logits if flags else logits
+            assert np.array_equal(plan.logits.numpy(), want)
