@@ -186,32 +186,24 @@ struct RowCtx {
     const uint32_t* bm;   // bitmap, bit e set: column e is penalised
 };
 
-// Widen one vector, blank the lanes outside the row (NaN never passes a filter and is
-// ignored by fmaxf), apply the penalty from the bitmap, scale by 1/temperature.
+__device__ __forceinline__ bool bm_test(const uint32_t* bm, int e) { return (bm[e >> 5] >> (e & 31)) & 1u; }
+
+// The largest scaled value of one complete vector, with the penalty applied to the flagged
+// columns: used for the first region only, whose thread-maxima seed the threshold.
 template <typename T>
-__device__ __forceinline__ void decode_vec(const uint4& raw, int vec, const RowCtx& c, float* v) {
+__device__ __forceinline__ float vec_max_penalised(const uint4& rawv, int vec, const RowCtx& c) {
     constexpr int VEC = Elem<T>::VEC;
-    Elem<T>::widen(raw, v);
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
     const int e0 = vec * VEC - c.mis;
-    const bool edge = (vec == 0 && c.mis != 0) || vec >= c.last_vec;
-    if (edge) {
+    float m = __uint_as_float(0xff800000u);
 #pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            int e = e0 + j;
-            bool ok = e >= 0 && e < c.V;
-            if (ok && c.pen_bitmap && ((c.bm[e >> 5] >> (e & 31)) & 1u)) v[j] = penalise(v[j], c.pen);
-            if (!ok) v[j] = __uint_as_float(0x7fc00000u);
-        }
-    } else if (c.pen_bitmap) {
-        uint32_t bits = __funnelshift_r(c.bm[e0 >> 5], c.bm[(e0 >> 5) + 1], e0 & 31) & ((1u << VEC) - 1u);
-        if (bits) {
-#pragma unroll
-            for (int j = 0; j < VEC; j++)
-                if ((bits >> j) & 1u) v[j] = penalise(v[j], c.pen);
-        }
+    for (int j = 0; j < VEC; j++) {
+        float l = raw[j];
+        if (c.pen_bitmap && bm_test(c.bm, e0 + j)) l = penalise(l, c.pen);
+        m = fmaxf(m, __fmul_rn(l, c.inv_temp));
     }
-#pragma unroll
-    for (int j = 0; j < VEC; j++) v[j] = __fmul_rn(v[j], c.inv_temp);
+    return m;
 }
 
 __device__ __forceinline__ int live_count(const Ctl* ctl) {
@@ -225,6 +217,41 @@ __device__ __forceinline__ void append(Cand* buf, Ctl* ctl, float v, int gidx) {
         e.key = f2key(v);
         e.idx = (uint32_t)gidx;
         buf[slot] = e;
+    }
+}
+
+// One column whose scaled RAW value reached the filter.  The penalty only ever lowers a
+// logit (l/p < l for l > 0, l*p < l for l < 0, p > 1), so filtering raw values first is
+// conservative: only here, on the rare survivor, is the bitmap consulted, the penalty
+// applied and the filter repeated on the true value.
+template <bool INCL>
+__device__ __forceinline__ void consider(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, float v, int e, float thr) {
+    if (c.pen_bitmap && bm_test(c.bm, e)) {
+        v = __fmul_rn(penalise(raw, c.pen), c.inv_temp);
+        if (!(INCL ? v >= thr : v > thr)) return;
+    }
+    append(buf, ctl, v, e + c.voff);
+}
+
+// The hot loop body: one complete 16-byte vector.  Scale, take the maximum, and leave
+// unless some column reaches the threshold (NaN never does; fmaxf ignores it).
+template <typename T, bool INCL>
+__device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const RowCtx& c, float thr, Cand* buf,
+                                           Ctl* ctl) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC], x[VEC];
+    Elem<T>::widen(rawv, raw);
+    float m = __uint_as_float(0xff800000u);
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+        x[j] = __fmul_rn(raw[j], c.inv_temp);
+        m = fmaxf(m, x[j]);
+    }
+    if (INCL ? m >= thr : m > thr) {
+        const int e0 = vec * VEC - c.mis;
+#pragma unroll
+        for (int j = 0; j < VEC; j++)
+            if (INCL ? x[j] >= thr : x[j] > thr) consider<INCL>(buf, ctl, c, raw[j], x[j], e0 + j, thr);
     }
 }
 
@@ -400,6 +427,43 @@ __device__ uint32_t select_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int 
     __syncthreads();
     *have_kth = true;
     return kth;
+}
+
+// Exact cut for a small buffer (n <= RANK_MAX entries): every entry counts the entries that
+// precede it in the order (key descending, index ascending) and moves to that position,
+// which leaves the best min(k, n) entries in order.  Two barriers, no atomics.
+constexpr int RANK_MAX = 256;
+
+__device__ uint32_t rank_select(Cand* buf, Ctl* ctl, int n, int k, int tid, bool* have_kth) {
+    Cand me;
+    me.key = 0;
+    me.idx = 0;
+    int rank = 0x7fffffff;
+    if (tid < n) {
+        me = buf[tid];
+        rank = 0;
+        for (int j = 0; j < n; j++) {
+            Cand o = buf[j];
+            rank += (o.key > me.key || (o.key == me.key && o.idx < me.idx)) ? 1 : 0;
+        }
+    }
+    __syncthreads();
+    if (rank < k) buf[rank] = me;
+    if (rank == k - 1) ctl->sel_bin = (int)me.key;
+    if (tid == 0) ctl->cnt = min(n, k);
+    __syncthreads();
+    *have_kth = n >= k;
+    return (uint32_t)ctl->sel_bin;
+}
+
+// Cut the buffer to its k best entries, by counting when it is small and by radix select
+// otherwise.  Called by every thread with the buffer quiescent.
+__device__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid, bool* have_kth) {
+    __syncthreads();
+    const int n = live_count(ctl);
+    __syncthreads();
+    if (n <= RANK_MAX) return rank_select(buf, ctl, n, k, tid, have_kth);
+    return select_topk(buf, ctl, hist, k, tid, have_kth);
 }
 
 // Orders the n <= KMAX entries of the buffer (key descending, index ascending) by
@@ -668,43 +732,44 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
     __syncthreads();
 
     // ---- stream the row ------------------------------------------------------------------
+    // Vectors [a0, b0) of this CTA's share lie wholly inside the row; the columns of the (at
+    // most two) partial vectors at the row's ends are taken one by one afterwards.
     const uint4* vbase = reinterpret_cast<const uint4*>(c.base16);
     constexpr int RV = NT * U;  // vectors per region
-    const int nreg = (vhi - vlo + RV - 1) / RV;
-    float thr = __uint_as_float(0xff800000u);  // -inf
-    bool careful = (k > 32 * NWARP) || nreg == 0;
+    const int a0 = max(vlo, c.mis != 0 ? 1 : 0);
+    const int b0 = min(vhi, (c.mis + c.V) / VEC);
+    const int nreg = b0 > a0 ? (b0 - a0 + RV - 1) / RV : 0;
+    const int trig = min(k + max(k >> 1, 16), CAP / 2);  // refresh the threshold after this many entries
+    float thr = __uint_as_float(0xff800000u);            // -inf
+    bool careful = k > 32 * NWARP;
 
     uint4 cur[U], nxt[U];
-    if (!careful) {
+    if (!careful && nreg > 0) {
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            int v = vlo + u * NT + tid;
-            cur[u] = v < vhi ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+            int v = a0 + u * NT + tid;
+            cur[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
         }
     }
     for (int r = 0; r < nreg && !careful; r++) {
-        const int v0 = vlo + r * RV + tid;
-        if (r + 1 < nreg) {
+        const int v0 = a0 + r * RV + tid;
+        const bool full = r + 1 < nreg;  // only the last region can be partial
+        if (full) {
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 int v = v0 + RV + u * NT;
-                nxt[u] = v < vhi ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+                nxt[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
             }
         }
         if (r == 0) {
-            // A threshold that at least k elements of this region reach: with
+            // A threshold that at least k columns of this region reach: with
             // j = ceil(k / warps), every warp holds j thread-maxima >= its j-th largest one,
-            // so the smallest of those per-warp values is reached by >= k elements.
+            // so the smallest of those per-warp values is reached by >= k columns.
             float tmax = __uint_as_float(0xff800000u);
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 int v = v0 + u * NT;
-                if (v < vhi) {
-                    float x[VEC];
-                    decode_vec<T>(cur[u], v, c, x);
-#pragma unroll
-                    for (int j = 0; j < VEC; j++) tmax = fmaxf(tmax, x[j]);
-                }
+                if (v < b0) tmax = fmaxf(tmax, vec_max_penalised<T>(cur[u], v, c));
             }
             float x = tmax;  // bitonic sort across the warp, descending
 #pragma unroll
@@ -728,42 +793,53 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 int v = v0 + u * NT;
-                if (v < vhi) {
-                    float xv[VEC];
-                    decode_vec<T>(cur[u], v, c, xv);
-#pragma unroll
-                    for (int j3 = 0; j3 < VEC; j3++)
-                        if (xv[j3] >= thr) append(buf, ctl, xv[j3], v * VEC - c.mis + j3 + c.voff);
-                }
+                if (v < b0) filter_vec<T, true>(cur[u], v, c, thr, buf, ctl);
             }
-        } else {
+        } else if (full) {
             // Later columns: the buffer already holds k entries >= thr with lower indices, so
             // an equal value can no longer enter (sampler.go:268-275): strict compare.
 #pragma unroll
+            for (int u = 0; u < U; u++) filter_vec<T, false>(cur[u], v0 + u * NT, c, thr, buf, ctl);
+        } else {
+#pragma unroll
             for (int u = 0; u < U; u++) {
                 int v = v0 + u * NT;
-                if (v < vhi) {
-                    float xv[VEC];
-                    decode_vec<T>(cur[u], v, c, xv);
-#pragma unroll
-                    for (int j3 = 0; j3 < VEC; j3++)
-                        if (xv[j3] > thr) append(buf, ctl, xv[j3], v * VEC - c.mis + j3 + c.voff);
-                }
+                if (v < b0) filter_vec<T, false>(cur[u], v, c, thr, buf, ctl);
             }
         }
         // One barrier per region.  The thread that made the last append of the region reads
         // the final count before it arrives, so the OR is the same for every thread.
-        if (__syncthreads_or(live_count(ctl) > CAP / 2)) {
+        const int lim = r == 0 ? k + 1 : trig;
+        if (__syncthreads_or(live_count(ctl) >= lim)) {
             if (live_count(ctl) > CAP) {
                 careful = true;  // entries were dropped: start over on the careful path
-            } else if (r + 1 < nreg) {
+            } else {
                 bool have;
-                uint32_t kth = select_topk(buf, ctl, hist, k, tid, &have);
+                uint32_t kth = refresh_topk(buf, ctl, hist, k, tid, &have);
                 if (have) thr = key2f(kth);
             }
         }
 #pragma unroll
         for (int u = 0; u < U; u++) cur[u] = nxt[u];
+    }
+
+    if (!careful) {
+        // the columns of the partial vectors at the ends of this CTA's share
+        int r1_lo = elo, r1_hi = ehi, r2_lo = ehi, r2_hi = ehi;
+        if (b0 > a0) {
+            r1_hi = min(ehi, max(elo, a0 * VEC - c.mis));
+            r2_lo = max(elo, b0 * VEC - c.mis);
+        }
+        const int n1 = r1_hi - r1_lo, n2 = r2_hi - r2_lo;
+        if (tid < n1 + n2) {  // at most 4 * VEC columns
+            int e = tid < n1 ? r1_lo + tid : r2_lo + (tid - n1);
+            float raw = Elem<T>::load1(c.row, e);
+            float v = __fmul_rn(raw, c.inv_temp);
+            if (v >= thr) consider<true>(buf, ctl, c, raw, v, e, thr);
+        }
+        __syncthreads();
+        if (live_count(ctl) > CAP) careful = true;
+        __syncthreads();
     }
 
     if (careful) {
@@ -793,7 +869,7 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
                 int e = e0 + j * NT + tid;
                 if (e < ehi) {
                     float l = Elem<T>::load1(c.row, e);
-                    if (c.pen_bitmap && ((bm[e >> 5] >> (e & 31)) & 1u)) l = penalise(l, c.pen);
+                    if (c.pen_bitmap && bm_test(bm, e)) l = penalise(l, c.pen);
                     float v = __fmul_rn(l, c.inv_temp);
                     if (strict ? (v > thr) : (v >= thr)) append(buf, ctl, v, e + c.voff);
                 }
@@ -804,7 +880,7 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
 
     // ---- cut to k, order, finish ------------------------------------------------------------
     bool have;
-    select_topk(buf, ctl, hist, k, tid, &have);
+    refresh_topk(buf, ctl, hist, k, tid, &have);
     __syncthreads();
     if (bad_k) {
         if (tid == 0) {
