@@ -23,19 +23,36 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "../../include/mantle_cuda_sampler.h"
 
 namespace {
 
-constexpr int NT = 512;              // threads per CTA
-constexpr int NWARP = NT / 32;
-constexpr int U = 4;                 // 16-byte vectors per thread per region
-constexpr int CAP = 4096;            // candidate buffer entries
 constexpr int KMAX = MANTLE_SAMPLE_MAX_TOP_K;
-constexpr int EPT = CAP / NT;        // candidate entries per thread during compaction
-constexpr int SLOW_EPT = 4;          // elements per thread per step of the careful path
-static_assert(KMAX + NT * SLOW_EPT <= CAP, "careful path needs room for one full step");
+constexpr int SLOW_EPT = 4;   // columns per thread per step of the careful path
+constexpr int RANK_MAX = 256; // largest buffer the counting select takes
+
+// Launch shape of one kernel instantiation.
+//   NT    threads per CTA            U     16-byte vectors per thread per region
+//   CAP   candidate buffer entries   KCAP  largest top_k this shape serves
+//   MINB  CTAs per SM the register budget is held to
+template <int NT_, int U_, int CAP_, int KCAP_, int MINB_>
+struct Shape {
+    static constexpr int NT = NT_, U = U_, CAP = CAP_, KCAP = KCAP_, MINB = MINB_;
+    static constexpr int NWARP = NT / 32;
+    static constexpr int EPT = CAP / NT;  // candidate entries per thread during compaction
+    static_assert(KCAP + NT * SLOW_EPT <= CAP, "careful path needs room for one full step");
+    static_assert(KCAP * 24 <= CAP * 8, "ordered shortlist must fit behind the survivors");
+    static_assert(RANK_MAX <= NT, "counting select: one entry per thread");
+    // shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [bitmap words]
+    static constexpr size_t SMEM_FIXED = 8 * (size_t)CAP + 4 * 256 + 512;
+};
+using ShapeSmallK = Shape<256, 4, 2048, 256, 4>;   // top_k <= 256: four CTAs per SM
+using ShapeLargeK = Shape<512, 4, 4096, KMAX, 2>;  // top_k <= 1024: two CTAs per SM
+constexpr int MAX_NWARP = 32;
+constexpr int MERGE_CAP = ShapeLargeK::CAP;
 
 constexpr int MODE_FUSED = 0;    // one CTA per row, tail in the same kernel
 constexpr int MODE_PARTS = 1;    // several CTAs per row (or one vocabulary shard): write the local shortlist
@@ -59,10 +76,11 @@ struct Ctl {
     int pad;
     double sum;
     double new_sum;
-    float warpv[NWARP];
-    uint32_t warpk_min[NWARP];
-    uint32_t warpk_max[NWARP];
+    float warpv[MAX_NWARP];
+    uint32_t warpk_min[MAX_NWARP];
+    uint32_t warpk_max[MAX_NWARP];
 };
+static_assert(sizeof(Ctl) <= 512, "control block outgrew its slot");
 
 struct KArgs {
     const void* logits;
@@ -174,19 +192,45 @@ struct Elem<bf16_t> {
 
 // What a CTA knows about its row while it streams.
 struct RowCtx {
-    const char* base16;   // row pointer rounded down to 16 bytes
     const void* row;      // row pointer
-    int mis;              // elements between base16 and the row pointer
+    int mis;              // elements between the 16-byte boundary below the row pointer and the pointer
     int V;                // columns
-    int last_vec;         // index of the last 16-byte vector that holds a column
     int voff;             // global id of column 0
     float inv_temp;
     float pen;
-    bool pen_bitmap;      // apply the penalty from the bitmap while streaming
+    bool pen_bitmap;      // the penalty is applied from the bitmap (logits stay read-only)
     const uint32_t* bm;   // bitmap, bit e set: column e is penalised
 };
 
 __device__ __forceinline__ bool bm_test(const uint32_t* bm, int e) { return (bm[e >> 5] >> (e & 31)) & 1u; }
+
+__device__ __forceinline__ int live_count(const Ctl* ctl) {
+    return *reinterpret_cast<const volatile int*>(&ctl->cnt);
+}
+
+template <class S>
+__device__ __forceinline__ void append(Cand* buf, Ctl* ctl, float v, int gidx) {
+    int slot = atomicAdd(&ctl->cnt, 1);
+    if (slot < S::CAP) {
+        Cand e;
+        e.key = f2key(v);
+        e.idx = (uint32_t)gidx;
+        buf[slot] = e;
+    }
+}
+
+// One column whose scaled RAW value reached the filter.  The penalty only ever lowers a
+// logit (l/p < l for l > 0, l*p < l for l < 0, p > 1), so filtering raw values first is
+// conservative: only here, on the rare survivor, is the bitmap consulted, the penalty
+// applied and the filter repeated on the true value.
+template <class S, bool INCL>
+__device__ __forceinline__ void consider(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, float v, int e, float thr) {
+    if (c.pen_bitmap && bm_test(c.bm, e)) {
+        v = __fmul_rn(penalise(raw, c.pen), c.inv_temp);
+        if (!(INCL ? v >= thr : v > thr)) return;
+    }
+    append<S>(buf, ctl, v, e + c.voff);
+}
 
 // The largest scaled value of one complete vector, with the penalty applied to the flagged
 // columns: used for the first region only, whose thread-maxima seed the threshold.
@@ -206,52 +250,34 @@ __device__ __forceinline__ float vec_max_penalised(const uint4& rawv, int vec, c
     return m;
 }
 
-__device__ __forceinline__ int live_count(const Ctl* ctl) {
-    return *reinterpret_cast<const volatile int*>(&ctl->cnt);
-}
-
-__device__ __forceinline__ void append(Cand* buf, Ctl* ctl, float v, int gidx) {
-    int slot = atomicAdd(&ctl->cnt, 1);
-    if (slot < CAP) {
-        Cand e;
-        e.key = f2key(v);
-        e.idx = (uint32_t)gidx;
-        buf[slot] = e;
-    }
-}
-
-// One column whose scaled RAW value reached the filter.  The penalty only ever lowers a
-// logit (l/p < l for l > 0, l*p < l for l < 0, p > 1), so filtering raw values first is
-// conservative: only here, on the rare survivor, is the bitmap consulted, the penalty
-// applied and the filter repeated on the true value.
-template <bool INCL>
-__device__ __forceinline__ void consider(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, float v, int e, float thr) {
-    if (c.pen_bitmap && bm_test(c.bm, e)) {
-        v = __fmul_rn(penalise(raw, c.pen), c.inv_temp);
-        if (!(INCL ? v >= thr : v > thr)) return;
-    }
-    append(buf, ctl, v, e + c.voff);
-}
-
 // The hot loop body: one complete 16-byte vector.  Scale, take the maximum, and leave
-// unless some column reaches the threshold (NaN never does; fmaxf ignores it).
-template <typename T, bool INCL>
+// unless some column reaches the threshold (NaN never does; fmaxf ignores it).  The rare
+// survivors are walked one at a time so that the slow code exists once per vector.
+template <class S, typename T, bool INCL>
 __device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const RowCtx& c, float thr, Cand* buf,
                                            Ctl* ctl) {
     constexpr int VEC = Elem<T>::VEC;
-    float raw[VEC], x[VEC];
+    float raw[VEC];
     Elem<T>::widen(rawv, raw);
-    float m = __uint_as_float(0xff800000u);
+    float m = __fmul_rn(raw[0], c.inv_temp);
 #pragma unroll
-    for (int j = 0; j < VEC; j++) {
-        x[j] = __fmul_rn(raw[j], c.inv_temp);
-        m = fmaxf(m, x[j]);
-    }
+    for (int j = 1; j < VEC; j++) m = fmaxf(m, __fmul_rn(raw[j], c.inv_temp));
     if (INCL ? m >= thr : m > thr) {
-        const int e0 = vec * VEC - c.mis;
+        uint32_t pass = 0;
 #pragma unroll
-        for (int j = 0; j < VEC; j++)
-            if (INCL ? x[j] >= thr : x[j] > thr) consider<INCL>(buf, ctl, c, raw[j], x[j], e0 + j, thr);
+        for (int j = 0; j < VEC; j++) {
+            float x = __fmul_rn(raw[j], c.inv_temp);
+            pass |= (INCL ? x >= thr : x > thr) ? (1u << j) : 0u;
+        }
+        const int e0 = vec * VEC - c.mis;
+        while (pass) {
+            const int j = __ffs(pass) - 1;
+            pass &= pass - 1;
+            float r = raw[0];
+#pragma unroll
+            for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
+            consider<S, INCL>(buf, ctl, c, r, __fmul_rn(r, c.inv_temp), e0 + j, thr);
+        }
     }
 }
 
@@ -264,10 +290,12 @@ __device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const Row
 // Digits are taken from (key - smallest key), most significant first, so the first
 // histogram already spreads the candidates over up to 256 bins however narrow their
 // value range is.  Ties at the k-th key are resolved by a second select over the index.
-__device__ uint32_t select_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid, bool* have_kth) {
+template <class S>
+__device__ __noinline__ uint32_t select_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid, bool* have_kth) {
+    constexpr int NT = S::NT, NWARP = S::NWARP, EPT = S::EPT;
     const int lane = tid & 31, warp = tid >> 5;
     __syncthreads();
-    const int n = min(ctl->cnt, CAP);
+    const int n = min(live_count(ctl), S::CAP);
     __syncthreads();  // every thread has read the count before a caller may append again
     *have_kth = false;
     if (n <= k) return 0;
@@ -297,12 +325,11 @@ __device__ uint32_t select_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int 
         hi = max(hi, ctl->warpk_max[w]);
     }
     const uint32_t range = hi - lo;
-    int rem = 32 - __clz(range);  // significant bits of (key - lo); 0 when all keys are equal
-    if (range == 0) rem = 0;
+    int rem = range == 0 ? 0 : 32 - __clz(range);  // significant bits of (key - lo)
 
     int need = k;           // entries wanted among those matching the prefix
     int ties = n;           // entries matching the whole prefix so far
-    uint32_t prefix = 0;    // chosen high bits of (key - lo), right-aligned at bit `rem`
+    uint32_t prefix = 0;    // chosen high bits of (key - lo)
     while (rem > 0) {
         const int d = rem < 8 ? rem : 8;
         const int shift = rem - d;
@@ -310,8 +337,7 @@ __device__ uint32_t select_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int 
         __syncthreads();
         for (int i = tid; i < n; i += NT) {
             uint32_t o = buf[i].key - lo;
-            // the whole 32-bit shift by `rem` (== 32 on the first pass) must give 0
-            uint32_t hi_bits = rem >= 32 ? 0u : (o >> rem);
+            uint32_t hi_bits = rem >= 32 ? 0u : (o >> rem);  // a 32-bit shift by 32 must give 0
             if (hi_bits == prefix) atomicAdd(&hist[(o >> shift) & ((1u << d) - 1u)], 1u);
         }
         __syncthreads();
@@ -432,9 +458,7 @@ __device__ uint32_t select_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int 
 // Exact cut for a small buffer (n <= RANK_MAX entries): every entry counts the entries that
 // precede it in the order (key descending, index ascending) and moves to that position,
 // which leaves the best min(k, n) entries in order.  Two barriers, no atomics.
-constexpr int RANK_MAX = 256;
-
-__device__ uint32_t rank_select(Cand* buf, Ctl* ctl, int n, int k, int tid, bool* have_kth) {
+__device__ __forceinline__ uint32_t rank_select(Cand* buf, Ctl* ctl, int n, int k, int tid, bool* have_kth) {
     Cand me;
     me.key = 0;
     me.idx = 0;
@@ -458,19 +482,22 @@ __device__ uint32_t rank_select(Cand* buf, Ctl* ctl, int n, int k, int tid, bool
 
 // Cut the buffer to its k best entries, by counting when it is small and by radix select
 // otherwise.  Called by every thread with the buffer quiescent.
-__device__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid, bool* have_kth) {
+template <class S>
+__device__ __forceinline__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid,
+                                                 bool* have_kth) {
     __syncthreads();
     const int n = live_count(ctl);
     __syncthreads();
     if (n <= RANK_MAX) return rank_select(buf, ctl, n, k, tid, have_kth);
-    return select_topk(buf, ctl, hist, k, tid, have_kth);
+    return select_topk<S>(buf, ctl, hist, k, tid, have_kth);
 }
 
-// Orders the n <= KMAX entries of the buffer (key descending, index ascending) by
+// Orders the n <= KCAP entries of the buffer (key descending, index ascending) by
 // counting, into sval/sidx.  Entries are distinct under that order, so ranks are a
 // permutation.
+template <class S>
 __device__ void rank_sort(const Cand* buf, int n, float* sval, int32_t* sidx, int tid) {
-    for (int i = tid; i < n; i += NT) {
+    for (int i = tid; i < n; i += S::NT) {
         Cand me = buf[i];
         int rank = 0;
         for (int j = 0; j < n; j++) {
@@ -486,8 +513,10 @@ __device__ void rank_sort(const Cand* buf, int n, float* sval, int32_t* sidx, in
 // memory.  Probabilities are doubles summed in shortlist order by one thread, which is
 // what makes the result identical to the reference's; everything elementwise is spread
 // over the CTA.
+template <class S>
 __device__ void sample_tail(const KArgs& a, int row, const MantleSampleParams& P, bool greedy, int n,
                             float* sval, int32_t* sidx, double* sprob, Ctl* ctl, int tid) {
+    constexpr int NT = S::NT;
     if (n == 0) {  // only an all-NaN row ends here; the reference's behaviour there is undefined
         if (tid == 0) {
             a.next[row] = 0;
@@ -595,29 +624,27 @@ __device__ void sample_tail(const KArgs& a, int row, const MantleSampleParams& P
     }
 }
 
-// Shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [bitmap words]
-constexpr size_t SMEM_FIXED = sizeof(Cand) * CAP + sizeof(uint32_t) * 256 + sizeof(Ctl);
-
 __host__ __device__ inline size_t bitmap_words(int vocab) { return (size_t)((vocab + 31) / 32 + 2); }
 
 // After the select: order the survivors and either finish the row or publish the local
 // shortlist.  The ordered arrays live in the part of the candidate buffer the survivors
-// (at most KMAX entries) do not occupy.
-template <int MODE>
+// (at most KCAP entries) do not occupy.
+template <class S, int MODE>
 __device__ void finish_row(const KArgs& a, int row, int split, const MantleSampleParams& P, bool greedy,
                            Cand* buf, Ctl* ctl, int tid) {
-    const int n = min(ctl->cnt, KMAX);
-    float* sval = reinterpret_cast<float*>(buf + KMAX);
-    int32_t* sidx = reinterpret_cast<int32_t*>(sval + KMAX);
-    double* sprob = reinterpret_cast<double*>(sidx + KMAX);
-    rank_sort(buf, n, sval, sidx, tid);
+    constexpr int KC = S::KCAP;
+    const int n = min(ctl->cnt, KC);
+    float* sval = reinterpret_cast<float*>(buf + KC);
+    int32_t* sidx = reinterpret_cast<int32_t*>(sval + KC);
+    double* sprob = reinterpret_cast<double*>(sidx + KC);
+    rank_sort<S>(buf, n, sval, sidx, tid);
     __syncthreads();
     if (MODE == MODE_FUSED) {
-        sample_tail(a, row, P, greedy, n, sval, sidx, sprob, ctl, tid);
+        sample_tail<S>(a, row, P, greedy, n, sval, sidx, sprob, ctl, tid);
     } else {
         const size_t base = ((size_t)split * a.rows + row) * a.part_cap;
         const int m = min(n, a.part_cap);
-        for (int i = tid; i < m; i += NT) {
+        for (int i = tid; i < m; i += S::NT) {
             a.part_val[base + i] = sval[i];
             a.part_idx[base + i] = sidx[i];
         }
@@ -625,68 +652,94 @@ __device__ void finish_row(const KArgs& a, int row, int split, const MantleSampl
     }
 }
 
+__device__ __forceinline__ MantleSampleParams row_params(const KArgs& a, int row) {
+    MantleSampleParams P;
+    if (a.params) {
+        P = a.params[row];
+    } else {  // plain argmax of every row
+        P.temperature = 1.0f; P.top_p = 1.0f; P.min_p = 0.0f; P.repeat_penalty = 1.0f;
+        P.top_k = 1; P.repeat_last_n = 1; P.greedy = 1; P.reserved = 0; P.uniform = 0.0;
+    }
+    return P;
+}
+
 // ---------------------------------------------------------------------------------------
 // The streaming kernel.
 
-template <typename T, int MODE>
-__global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
+template <class S, typename T, int MODE>
+__global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_kernel(const KArgs a) {
     constexpr int VEC = Elem<T>::VEC;
+    constexpr int NT = S::NT, NWARP = S::NWARP, U = S::U, CAP = S::CAP;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Cand* buf = reinterpret_cast<Cand*>(smem_raw);
     uint32_t* hist = reinterpret_cast<uint32_t*>(buf + CAP);
     Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
-    uint32_t* bm = reinterpret_cast<uint32_t*>(ctl + 1);
+    uint32_t* bm = reinterpret_cast<uint32_t*>(smem_raw + S::SMEM_FIXED);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row = blockIdx.x / a.splits;
     const int split = blockIdx.x - row * a.splits;
 
     // ---- the row's parameters --------------------------------------------------------
-    MantleSampleParams P;
-    if (a.params) {
-        P = a.params[row];
-    } else {
-        P.temperature = 1.0f; P.top_p = 1.0f; P.min_p = 0.0f; P.repeat_penalty = 1.0f;
-        P.top_k = 1; P.repeat_last_n = 1; P.greedy = 1; P.reserved = 0; P.uniform = 0.0;
-    }
+    const MantleSampleParams P = row_params(a, row);
     // sampler.go:140: greedy, or the top-1 / top_p >= 1 / temperature == 1 shortcut
     const bool greedy = P.greedy != 0 || (P.top_k == 1 && P.top_p >= 1.0f && P.temperature == 1.0f);
     int k = greedy ? 1 : min(P.top_k, a.vocab_total);  // sampler.go:147
     bool bad_k = false;
-    if (!greedy && (k > a.max_top_k || k > KMAX || k < 1)) {
+    if (!greedy && (k > a.max_top_k || k > S::KCAP || k < 1)) {
         bad_k = true;
-        k = max(1, min(min(k, a.max_top_k), KMAX));
+        k = max(1, min(min(k, a.max_top_k), S::KCAP));
     }
 
     RowCtx c;
     c.row = reinterpret_cast<const T*>(a.logits) + (size_t)row * (size_t)a.row_stride;
     c.mis = (int)((reinterpret_cast<uintptr_t>(c.row) & 15u) / sizeof(T));
-    c.base16 = reinterpret_cast<const char*>(c.row) - (size_t)c.mis * sizeof(T);
     c.V = a.vocab;
     c.voff = a.vocab_offset;
     c.inv_temp = greedy ? 1.0f : __fdiv_rn(1.0f, P.temperature);  // sampler.go:144-145
     c.pen = P.repeat_penalty;
     c.bm = bm;
+    c.pen_bitmap = false;
+    const uint4* vbase = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(c.row) -
+                                                        (size_t)c.mis * sizeof(T));
     const int nvec = (c.mis + c.V + VEC - 1) / VEC;
-    c.last_vec = nvec - 1;
 
-    // this CTA's share of the row, in vectors and in columns
+    // This CTA's share of the row, in vectors and in columns.  Vectors [a0, b0) of the share
+    // lie wholly inside the row and are streamed; the columns of the (at most two) partial
+    // vectors at the row's ends are taken one by one afterwards.
     const int per = (nvec + a.splits - 1) / a.splits;
     const int vlo = min(split * per, nvec);
     const int vhi = min(vlo + per, nvec);
     const int elo = max(vlo * VEC - c.mis, 0);
     const int ehi = min(vhi * VEC - c.mis, c.V);
+    constexpr int RV = NT * U;  // vectors per region
+    const int a0 = max(vlo, c.mis != 0 ? 1 : 0);
+    const int b0 = min(vhi, (c.mis + c.V) / VEC);
+    const int nreg = b0 > a0 ? (b0 - a0 + RV - 1) / RV : 0;
 
-    if (tid == 0) ctl->cnt = 0;
-
-    // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
     int hl = 0;
     if (a.history && !(a.flags & MANTLE_SAMPLE_PENALTY_PREAPPLIED)) {
         hl = a.hist_len ? a.hist_len[row] : a.hist_stride;
         hl = max(0, min(hl, a.hist_stride));
     }
     const bool pen_active = P.repeat_penalty > 1.0f && hl > 0;
-    c.pen_bitmap = false;
+    const bool in_place = MODE == MODE_PENALTY || (a.flags & MANTLE_SAMPLE_WRITE_BACK_PENALTY) != 0;
+    bool careful = k > 32 * NWARP;
+
+    // The first region's loads go out before anything else, so that they are in flight while
+    // the bitmap is built -- unless the penalty is about to rewrite the row in place.
+    uint4 ra[U], rb[U];
+    const bool early = MODE != MODE_PENALTY && !careful && nreg > 0 && !(pen_active && in_place);
+    if (early) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            int v = a0 + u * NT + tid;
+            ra[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+        }
+    }
+    if (tid == 0) ctl->cnt = 0;
+
+    // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
     if (pen_active) {
         const int nwords = (int)bitmap_words(c.V);
         for (int w = tid; w < nwords; w += NT) bm[w] = 0;
@@ -701,7 +754,7 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
             }
         }
         __syncthreads();
-        for (int j = tid; j < a.n_exclude; j += NT) {
+        for (int j = tid; j < a.n_exclude; j += NT) {  // sampler.go:122-126
             int id = a.exclude[j];
             if (id >= 0 && id < a.vocab_total) {
                 id -= c.voff;
@@ -709,7 +762,7 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
             }
         }
         __syncthreads();
-        if (MODE == MODE_PENALTY || (a.flags & MANTLE_SAMPLE_WRITE_BACK_PENALTY)) {
+        if (in_place) {
             // the reference's in-place form: one read-modify-write per distinct id this CTA owns
             if (sizeof(T) == 4) {
                 float* wrow = const_cast<float*>(reinterpret_cast<const float*>(c.row));
@@ -723,7 +776,6 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
                     }
                 }
             }
-            __syncthreads();
         } else {
             c.pen_bitmap = true;
         }
@@ -732,45 +784,63 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
     __syncthreads();
 
     // ---- stream the row ------------------------------------------------------------------
-    // Vectors [a0, b0) of this CTA's share lie wholly inside the row; the columns of the (at
-    // most two) partial vectors at the row's ends are taken one by one afterwards.
-    const uint4* vbase = reinterpret_cast<const uint4*>(c.base16);
-    constexpr int RV = NT * U;  // vectors per region
-    const int a0 = max(vlo, c.mis != 0 ? 1 : 0);
-    const int b0 = min(vhi, (c.mis + c.V) / VEC);
-    const int nreg = b0 > a0 ? (b0 - a0 + RV - 1) / RV : 0;
-    const int trig = min(k + max(k >> 1, 16), CAP / 2);  // refresh the threshold after this many entries
+    const int trig = min(k + max(k >> 1, 16), CAP / 2);  // refresh the threshold at this many entries
     float thr = __uint_as_float(0xff800000u);            // -inf
-    bool careful = k > 32 * NWARP;
 
-    uint4 cur[U], nxt[U];
     if (!careful && nreg > 0) {
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            int v = a0 + u * NT + tid;
-            cur[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
-        }
-    }
-    for (int r = 0; r < nreg && !careful; r++) {
-        const int v0 = a0 + r * RV + tid;
-        const bool full = r + 1 < nreg;  // only the last region can be partial
-        if (full) {
+        if (!early) {
 #pragma unroll
             for (int u = 0; u < U; u++) {
-                int v = v0 + RV + u * NT;
-                nxt[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+                int v = a0 + u * NT + tid;
+                ra[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
             }
         }
-        if (r == 0) {
+        // `load(dst, r)`: region r into dst (predicated: only the last region can be partial)
+        auto load = [&](uint4(&dst)[U], int r) {
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                int v = a0 + r * RV + u * NT + tid;
+                dst[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+            }
+        };
+        // `later(src, r)`: regions after the first.  The buffer already holds k entries >= thr
+        // with lower indices, so an equal value can no longer enter (sampler.go:268-275).
+        auto later = [&](const uint4(&src)[U], int r) {
+            const int v0 = a0 + r * RV + tid;
+            if (r + 1 < nreg) {
+#pragma unroll
+                for (int u = 0; u < U; u++) filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (v0 + u * NT < b0) filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
+            }
+        };
+        // One barrier per region.  The thread that made the last append of the region reads
+        // the final count before it arrives, so the OR is the same for every thread.
+        auto region_end = [&](int lim) {
+            if (__syncthreads_or(live_count(ctl) >= lim)) {
+                if (live_count(ctl) > CAP) {
+                    careful = true;  // entries were dropped: start over on the careful path
+                } else {
+                    bool have;
+                    uint32_t kth = refresh_topk<S>(buf, ctl, hist, k, tid, &have);
+                    if (have) thr = key2f(kth);
+                }
+            }
+        };
+
+        // -- region 0 --
+        if (nreg > 1) load(rb, 1);
+        {
             // A threshold that at least k columns of this region reach: with
             // j = ceil(k / warps), every warp holds j thread-maxima >= its j-th largest one,
             // so the smallest of those per-warp values is reached by >= k columns.
+            const int v0 = a0 + tid;
             float tmax = __uint_as_float(0xff800000u);
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                int v = v0 + u * NT;
-                if (v < b0) tmax = fmaxf(tmax, vec_max_penalised<T>(cur[u], v, c));
-            }
+            for (int u = 0; u < U; u++)
+                if (v0 + u * NT < b0) tmax = fmaxf(tmax, vec_max_penalised<T>(ra[u], v0 + u * NT, c));
             float x = tmax;  // bitonic sort across the warp, descending
 #pragma unroll
             for (int k2 = 2; k2 <= 32; k2 <<= 1) {
@@ -791,36 +861,23 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
             for (int w = 1; w < NWARP; w++) t0 = fminf(t0, ctl->warpv[w]);
             thr = t0;
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                int v = v0 + u * NT;
-                if (v < b0) filter_vec<T, true>(cur[u], v, c, thr, buf, ctl);
-            }
-        } else if (full) {
-            // Later columns: the buffer already holds k entries >= thr with lower indices, so
-            // an equal value can no longer enter (sampler.go:268-275): strict compare.
-#pragma unroll
-            for (int u = 0; u < U; u++) filter_vec<T, false>(cur[u], v0 + u * NT, c, thr, buf, ctl);
-        } else {
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                int v = v0 + u * NT;
-                if (v < b0) filter_vec<T, false>(cur[u], v, c, thr, buf, ctl);
-            }
+            for (int u = 0; u < U; u++)
+                if (v0 + u * NT < b0) filter_vec<S, T, true>(ra[u], v0 + u * NT, c, thr, buf, ctl);
         }
-        // One barrier per region.  The thread that made the last append of the region reads
-        // the final count before it arrives, so the OR is the same for every thread.
-        const int lim = r == 0 ? k + 1 : trig;
-        if (__syncthreads_or(live_count(ctl) >= lim)) {
-            if (live_count(ctl) > CAP) {
-                careful = true;  // entries were dropped: start over on the careful path
-            } else {
-                bool have;
-                uint32_t kth = refresh_topk(buf, ctl, hist, k, tid, &have);
-                if (have) thr = key2f(kth);
-            }
+        region_end(k + 1);
+
+        // -- regions 1.. : two register sets, each refilled while the other is filtered --
+        int r = 1;
+        while (r < nreg && !careful) {
+            if (r + 1 < nreg) load(ra, r + 1);
+            later(rb, r);
+            region_end(trig);
+            if (++r >= nreg || careful) break;
+            if (r + 1 < nreg) load(rb, r + 1);
+            later(ra, r);
+            region_end(trig);
+            ++r;
         }
-#pragma unroll
-        for (int u = 0; u < U; u++) cur[u] = nxt[u];
     }
 
     if (!careful) {
@@ -835,7 +892,7 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
             int e = tid < n1 ? r1_lo + tid : r2_lo + (tid - n1);
             float raw = Elem<T>::load1(c.row, e);
             float v = __fmul_rn(raw, c.inv_temp);
-            if (v >= thr) consider<true>(buf, ctl, c, raw, v, e, thr);
+            if (v >= thr) consider<S, true>(buf, ctl, c, raw, v, e, thr);
         }
         __syncthreads();
         if (live_count(ctl) > CAP) careful = true;
@@ -845,8 +902,8 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
     if (careful) {
         // Careful path: any input, any order.  Steps of NT*SLOW_EPT columns with room for a
         // whole step guaranteed before it starts; the buffer is cut to k whenever it could
-        // overflow.  Reached for k > 512, for rows whose first region ties massively, and for
-        // adversarial orders (e.g. ascending logits).
+        // overflow.  Reached for k beyond 32 per warp, for rows whose first region ties
+        // massively, and for adversarial orders (e.g. ascending logits).
         __syncthreads();
         if (tid == 0) ctl->cnt = 0;
         __syncthreads();
@@ -857,7 +914,7 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
             __syncthreads();
             if (ctl->cnt + STEP > CAP) {
                 bool have;
-                uint32_t kth = select_topk(buf, ctl, hist, k, tid, &have);
+                uint32_t kth = select_topk<S>(buf, ctl, hist, k, tid, &have);
                 if (have) {
                     thr = key2f(kth);
                     strict = true;
@@ -871,7 +928,7 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
                     float l = Elem<T>::load1(c.row, e);
                     if (c.pen_bitmap && bm_test(bm, e)) l = penalise(l, c.pen);
                     float v = __fmul_rn(l, c.inv_temp);
-                    if (strict ? (v > thr) : (v >= thr)) append(buf, ctl, v, e + c.voff);
+                    if (strict ? (v > thr) : (v >= thr)) append<S>(buf, ctl, v, e + c.voff);
                 }
             }
         }
@@ -880,7 +937,7 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
 
     // ---- cut to k, order, finish ------------------------------------------------------------
     bool have;
-    refresh_topk(buf, ctl, hist, k, tid, &have);
+    refresh_topk<S>(buf, ctl, hist, k, tid, &have);
     __syncthreads();
     if (bad_k) {
         if (tid == 0) {
@@ -895,26 +952,21 @@ __global__ void __launch_bounds__(NT, 2) scan_rows_kernel(const KArgs a) {
         }
         return;
     }
-    finish_row<MODE>(a, row, split, P, greedy, buf, ctl, tid);
+    finish_row<S, MODE>(a, row, split, P, greedy, buf, ctl, tid);
 }
 
 // Merge of `parts` local shortlists per row (several CTAs of one GPU, or one per
 // vocabulary shard after an all-gather), then the tail.
-__global__ void __launch_bounds__(NT, 2) merge_parts_kernel(const KArgs a) {
+__global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_parts_kernel(const KArgs a) {
+    using S = ShapeLargeK;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Cand* buf = reinterpret_cast<Cand*>(smem_raw);
-    uint32_t* hist = reinterpret_cast<uint32_t*>(buf + CAP);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
     Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
     const int tid = threadIdx.x;
     const int row = blockIdx.x;
 
-    MantleSampleParams P;
-    if (a.params) {
-        P = a.params[row];
-    } else {
-        P.temperature = 1.0f; P.top_p = 1.0f; P.min_p = 0.0f; P.repeat_penalty = 1.0f;
-        P.top_k = 1; P.repeat_last_n = 1; P.greedy = 1; P.reserved = 0; P.uniform = 0.0;
-    }
+    const MantleSampleParams P = row_params(a, row);
     const bool greedy = P.greedy != 0 || (P.top_k == 1 && P.top_p >= 1.0f && P.temperature == 1.0f);
     int k = greedy ? 1 : min(P.top_k, a.vocab_total);
     const bool bad_k = !greedy && (k > a.max_top_k || k > KMAX || k < 1);
@@ -924,8 +976,8 @@ __global__ void __launch_bounds__(NT, 2) merge_parts_kernel(const KArgs a) {
     for (int p = 0; p < a.parts; p++) {
         const size_t slot = (size_t)p * a.rows + row;
         const int m = min(a.part_cnt[slot], a.part_cap);
-        for (int i = tid; i < m; i += NT)
-            append(buf, ctl, a.part_val[slot * a.part_cap + i], a.part_idx[slot * a.part_cap + i]);
+        for (int i = tid; i < m; i += S::NT)
+            append<S>(buf, ctl, a.part_val[slot * a.part_cap + i], a.part_idx[slot * a.part_cap + i]);
     }
     if (bad_k) {
         if (tid == 0) {
@@ -937,9 +989,9 @@ __global__ void __launch_bounds__(NT, 2) merge_parts_kernel(const KArgs a) {
         return;
     }
     bool have;
-    select_topk(buf, ctl, hist, k, tid, &have);
+    refresh_topk<S>(buf, ctl, hist, k, tid, &have);
     __syncthreads();
-    finish_row<MODE_FUSED>(a, row, 0, P, greedy, buf, ctl, tid);
+    finish_row<S, MODE_FUSED>(a, row, 0, P, greedy, buf, ctl, tid);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -974,14 +1026,29 @@ bool batch_ok(const MantleSampleBatch* b, bool need_outputs) {
     return true;
 }
 
+// Shape selection.  MANTLE_SAMPLER_SHAPE=small|large overrides it (a tuning aid: `small`
+// is refused, by falling back, for batches whose top_k it cannot serve).
+bool use_small_shape(int max_top_k) {
+    static const int forced = [] {
+        const char* e = getenv("MANTLE_SAMPLER_SHAPE");
+        if (!e) return 0;
+        return strcmp(e, "small") == 0 ? 1 : (strcmp(e, "large") == 0 ? 2 : 0);
+    }();
+    if (max_top_k > ShapeSmallK::KCAP) return false;
+    return forced != 2;
+}
+
 int choose_splits(const MantleSampleBatch* b) {
     const int vec = b->dtype == MANTLE_DTYPE_F32 ? 4 : 8;
     const int nvec = (b->vocab + vec - 1) / vec + 1;
-    const int max_by_k = CAP / b->max_top_k;  // the merge holds splits * k candidates
+    const bool small = use_small_shape(b->max_top_k);
+    const int region = small ? ShapeSmallK::NT * ShapeSmallK::U : ShapeLargeK::NT * ShapeLargeK::U;
+    const int per_sm = small ? ShapeSmallK::MINB : ShapeLargeK::MINB;
+    const int max_by_k = MERGE_CAP / b->max_top_k;  // the merge holds splits * k candidates
     if (b->splits > 0) return max(1, min(min(b->splits, max_by_k), min(nvec, 64)));
-    const int max_by_work = nvec / (2 * NT * U);  // at least two regions per CTA
+    const int max_by_work = nvec / (2 * region);  // at least two regions per CTA
     const int cap = max(1, min(min(max_by_k, max_by_work), 64));
-    const int target = 2 * sm_count();  // two CTAs per SM
+    const int target = per_sm * sm_count();  // one full wave
     if (b->rows >= target) return 1;
     return max(1, min(cap, (target + b->rows - 1) / b->rows));
 }
@@ -1017,20 +1084,31 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
 }
 
 template <typename K>
-int launch(K kernel, const KArgs& a, int grid, size_t smem, cudaStream_t stream) {
+int launch(K kernel, const KArgs& a, int grid, int threads, size_t smem, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    kernel<<<grid, NT, smem, stream>>>(a);
+    kernel<<<grid, threads, smem, stream>>>(a);
     return (int)cudaGetLastError();
+}
+
+template <class S, int MODE>
+int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
+    const size_t smem = S::SMEM_FIXED + bitmap_words(a.vocab) * sizeof(uint32_t);
+    const long long grid = (long long)a.rows * a.splits;
+    if (grid > 0x7fffffffLL) return kInvalid;
+    if (dtype == MANTLE_DTYPE_F32)
+        return launch(scan_rows_kernel<S, float, MODE>, a, (int)grid, S::NT, smem, stream);
+    return launch(scan_rows_kernel<S, bf16_t, MODE>, a, (int)grid, S::NT, smem, stream);
 }
 
 template <int MODE>
 int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
-    const size_t smem = SMEM_FIXED + bitmap_words(a.vocab) * sizeof(uint32_t);
-    const long long grid = (long long)a.rows * a.splits;
-    if (grid > 0x7fffffffLL) return kInvalid;
-    if (dtype == MANTLE_DTYPE_F32) return launch(scan_rows_kernel<float, MODE>, a, (int)grid, smem, stream);
-    return launch(scan_rows_kernel<bf16_t, MODE>, a, (int)grid, smem, stream);
+    if (use_small_shape(a.max_top_k)) return launch_scan_shape<ShapeSmallK, MODE>(a, dtype, stream);
+    return launch_scan_shape<ShapeLargeK, MODE>(a, dtype, stream);
+}
+
+int launch_merge(const KArgs& a, cudaStream_t stream) {
+    return launch(merge_parts_kernel, a, a.rows, ShapeLargeK::NT, ShapeLargeK::SMEM_FIXED, stream);
 }
 
 size_t parts_bytes(int rows, int parts, int cap) {
@@ -1077,7 +1155,7 @@ extern "C" int mantleCudaSampleRows(const MantleSampleBatch* batch, void* worksp
     a.part_cnt = a.part_idx + n * a.part_cap;
     int rc = launch_scan<MODE_PARTS>(a, batch->dtype, stream);
     if (rc) return rc;
-    return launch(merge_parts_kernel, a, batch->rows, SMEM_FIXED, stream);
+    return launch_merge(a, stream);
 }
 
 extern "C" int mantleCudaRepeatPenaltyRowsF32(const MantleSampleBatch* batch, mantleCudaStream_t stream_) {
@@ -1085,7 +1163,7 @@ extern "C" int mantleCudaRepeatPenaltyRowsF32(const MantleSampleBatch* batch, ma
     if (batch->flags & MANTLE_SAMPLE_PENALTY_PREAPPLIED) return kInvalid;
     KArgs a;
     fill_args(a, batch);
-    a.max_top_k = KMAX;
+    a.max_top_k = 1;
     return launch_scan<MODE_PENALTY>(a, MANTLE_DTYPE_F32, static_cast<cudaStream_t>(stream_));
 }
 
@@ -1132,7 +1210,7 @@ extern "C" int mantleCudaSampleMergeParts(const MantleSampleBatch* batch, int pa
     if (batch->max_top_k < 1 || batch->max_top_k > KMAX) return kInvalid;
     if ((batch->cand_idx || batch->cand_prob) && batch->cand_stride <= 0) return kInvalid;
     if (parts < 1 || !part_val || !part_idx || !part_cnt || part_cap < 1) return kInvalid;
-    if ((long long)parts * (part_cap < batch->max_top_k ? part_cap : batch->max_top_k) > CAP) return kInvalid;
+    if ((long long)parts * (part_cap < batch->max_top_k ? part_cap : batch->max_top_k) > MERGE_CAP) return kInvalid;
     if (batch->vocab <= 0) return kInvalid;
     KArgs a;
     fill_args(a, batch);
@@ -1141,7 +1219,7 @@ extern "C" int mantleCudaSampleMergeParts(const MantleSampleBatch* batch, int pa
     a.part_val = const_cast<float*>(part_val);
     a.part_idx = const_cast<int32_t*>(part_idx);
     a.part_cnt = const_cast<int32_t*>(part_cnt);
-    return launch(merge_parts_kernel, a, batch->rows, SMEM_FIXED, static_cast<cudaStream_t>(stream_));
+    return launch_merge(a, static_cast<cudaStream_t>(stream_));
 }
 
 // ---------------------------------------------------------------------------------------

@@ -203,9 +203,9 @@ def test_config_mixed_batch():
 
 def test_config_throughput_slice():
     w = workloads.make("throughput", rows=512, device=DEV)
-    g, _ = check_against_oracle(w.logits.cpu().numpy(), w.params, w.max_top_k, history=w.history.cpu().numpy(),
-                                cand_cap=20)
-    assert g["splits"] == 1
+    for splits in (1, 0):
+        check_against_oracle(w.logits.cpu().numpy(), w.params, w.max_top_k, history=w.history.cpu().numpy(),
+                             cand_cap=20, splits=splits)
 
 
 def test_full_size_properties():
