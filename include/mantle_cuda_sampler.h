@@ -57,6 +57,8 @@ typedef void* mantleCudaStream_t; /* a cudaStream_t, as in native/softmax.h:11 *
 #define MANTLE_SAMPLE_STATUS_TOPK_RANGE 1  /* a row's top_k exceeded max_top_k          */
 #define MANTLE_SAMPLE_STATUS_EMPTY 2       /* a row ended with an empty shortlist (the  */
                                            /* reference panics there); its token is -1  */
+#define MANTLE_SAMPLE_STATUS_TIMEOUT 4     /* a bounded wait on an asynchronous copy ran */
+                                           /* out; the launch stopped early              */
 
 /*
  * One batch of rows.  All pointers are device pointers on the current device.

@@ -26,37 +26,55 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
+
 #include "../../include/mantle_cuda_sampler.h"
+
+// Development aid, compiled out of the shipped library: with -DMANTLE_DEBUG_SWITCHES the
+// environment variable MANTLE_SAMPLER_DEBUG switches pieces of the kernel off to cost them.
+#ifdef MANTLE_DEBUG_SWITCHES
+#define DEBUG_OFF(a, bit) (((a).debug >> (bit)) & 1)
+#else
+#define DEBUG_OFF(a, bit) 0
+#endif
 
 namespace {
 
 constexpr int KMAX = MANTLE_SAMPLE_MAX_TOP_K;
-constexpr int SLOW_EPT = 4;   // columns per thread per step of the careful path
-constexpr int RANK_MAX = 256; // largest buffer the counting select takes
+constexpr int RANK_MAX = 256;  // largest buffer the counting select takes
+constexpr int HIST_CAP = 1024; // history-window ids staged in shared memory ahead of their row
+constexpr int MAX_STAGES = 8;
 
 // Launch shape of one kernel instantiation.
-//   NT    threads per CTA            U     16-byte vectors per thread per region
+//   NT    threads per CTA            U     16-byte vectors per thread per chunk
 //   CAP   candidate buffer entries   KCAP  largest top_k this shape serves
 //   MINB  CTAs per SM the register budget is held to
 template <int NT_, int U_, int CAP_, int KCAP_, int MINB_>
 struct Shape {
     static constexpr int NT = NT_, U = U_, CAP = CAP_, KCAP = KCAP_, MINB = MINB_;
     static constexpr int NWARP = NT / 32;
-    static constexpr int EPT = CAP / NT;  // candidate entries per thread during compaction
+    static constexpr int EPT = (CAP + NT - 1) / NT;  // candidate entries per thread during compaction
+    // columns per thread per step of the careful path: a whole step always fits the buffer
+    static constexpr int SLOW_EPT = (CAP - KCAP) / NT < 4 ? (CAP - KCAP) / NT : 4;
+    static_assert(SLOW_EPT >= 1, "careful path needs room");
     static_assert(KCAP + NT * SLOW_EPT <= CAP, "careful path needs room for one full step");
     static_assert(KCAP * 24 <= CAP * 8, "ordered shortlist must fit behind the survivors");
     static_assert(RANK_MAX <= NT, "counting select: one entry per thread");
-    // shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [bitmap words]
-    static constexpr size_t SMEM_FIXED = 8 * (size_t)CAP + 4 * 256 + 512;
+    // shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [Pre] [window ids[HIST_CAP]] [ring] [bitmap]
+    static constexpr size_t SMEM_FIXED = 8 * (size_t)CAP + 4 * 256 + 512 + 256 + 4 * (size_t)HIST_CAP;
 };
-using ShapeSmallK = Shape<256, 4, 2048, 256, 4>;   // top_k <= 256: four CTAs per SM
-using ShapeLargeK = Shape<512, 4, 4096, KMAX, 2>;  // top_k <= 1024: two CTAs per SM
+// Chunks are 32 KB: measured on B200, the time one bulk copy takes to land hardly depends on
+// its size (about 0.6 us for 8, 16 and 32 KB alike), so large chunks are what carries the
+// bandwidth; two stages per CTA and two CTAs per SM reached 7.3 TB/s in a bare copy loop.
+// 256 threads x 8 vectors leaves every thread 128 registers, so nothing spills.
+using ShapeSmallK = Shape<256, 8, 2048, 256, 2>;   // top_k <= 256: 16 KB candidate buffer
+using ShapeLargeK = Shape<512, 4, 4096, KMAX, 1>;  // top_k <= 1024: 32 KB candidate buffer
+using ShapeAlt = Shape<512, 4, 2048, 256, 2>;      // tuning: MANTLE_SAMPLER_SHAPE=alt
 constexpr int MAX_NWARP = 32;
 constexpr int MERGE_CAP = ShapeLargeK::CAP;
 
 constexpr int MODE_FUSED = 0;    // one CTA per row, tail in the same kernel
 constexpr int MODE_PARTS = 1;    // several CTAs per row (or one vocabulary shard): write the local shortlist
-constexpr int MODE_PENALTY = 2;  // repeat penalty only, in place
 
 struct Cand {
     uint32_t key;  // order-preserving image of the scaled value
@@ -79,8 +97,26 @@ struct Ctl {
     float warpv[MAX_NWARP];
     uint32_t warpk_min[MAX_NWARP];
     uint32_t warpk_max[MAX_NWARP];
+    uint64_t full[MAX_STAGES];  // one mbarrier per ring stage: "the chunk has landed"
+    int abort;                  // a wait on a copy ran out
 };
-static_assert(sizeof(Ctl) <= 512, "control block outgrew its slot");
+static_assert(sizeof(Ctl) <= 512 && sizeof(Ctl) % 8 == 0, "control block outgrew its slot");
+
+// What thread 0 fetches ahead for the item after the current one -- its parameters and history
+// length (small asynchronous copies) and, tracked by `win_full`, its history window -- and the
+// producer's own state, kept here rather than in registers that every thread would set aside.
+struct Pre {
+    MantleSampleParams p[2];
+    int hl[2];
+    int pad[2];
+    uint64_t win_full;
+    uint64_t pol;          // L2 eviction policy of the bulk copies
+    const uint4* p_vbase;  // item being issued: its row rounded down to 16 bytes,
+    int p_item, p_chunk, p_nchunks, p_a0, p_b0;  // its id, next chunk, chunk count, vector range
+    uint32_t g_issued;     // chunks issued so far
+    uint32_t w_issued;     // staged windows requested so far
+};
+static_assert(sizeof(Pre) <= 256, "prefetch block outgrew its slot");
 
 struct KArgs {
     const void* logits;
@@ -111,6 +147,10 @@ struct KArgs {
     int32_t* part_cnt;
     int part_cap;
     int parts;
+    int hist_tma_ok;  // history base 16-byte aligned and hist_stride a multiple of 4
+#ifdef MANTLE_DEBUG_SWITCHES
+    int debug;
+#endif
 };
 
 // ---------------------------------------------------------------------------------------
@@ -250,34 +290,40 @@ __device__ __forceinline__ float vec_max_penalised(const uint4& rawv, int vec, c
     return m;
 }
 
-// The hot loop body: one complete 16-byte vector.  Scale, take the maximum, and leave
-// unless some column reaches the threshold (NaN never does; fmaxf ignores it).  The rare
-// survivors are walked one at a time so that the slow code exists once per vector.
+// The largest scaled value of one complete vector (no penalty: raw values bound the true ones).
+template <typename T>
+__device__ __forceinline__ float vec_max_scaled(const uint4& rawv, float inv_temp) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    float m = __fmul_rn(raw[0], inv_temp);
+#pragma unroll
+    for (int j = 1; j < VEC; j++) m = fmaxf(m, __fmul_rn(raw[j], inv_temp));
+    return m;
+}
+
+// One complete 16-byte vector that may hold a survivor.  Survivors are walked one at a time
+// (NaN never passes a compare), so the slow code exists once per call site.
 template <class S, typename T, bool INCL>
 __device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const RowCtx& c, float thr, Cand* buf,
                                            Ctl* ctl) {
     constexpr int VEC = Elem<T>::VEC;
     float raw[VEC];
     Elem<T>::widen(rawv, raw);
-    float m = __fmul_rn(raw[0], c.inv_temp);
+    uint32_t pass = 0;
 #pragma unroll
-    for (int j = 1; j < VEC; j++) m = fmaxf(m, __fmul_rn(raw[j], c.inv_temp));
-    if (INCL ? m >= thr : m > thr) {
-        uint32_t pass = 0;
+    for (int j = 0; j < VEC; j++) {
+        float x = __fmul_rn(raw[j], c.inv_temp);
+        pass |= (INCL ? x >= thr : x > thr) ? (1u << j) : 0u;
+    }
+    const int e0 = vec * VEC - c.mis;
+    while (pass) {
+        const int j = __ffs(pass) - 1;
+        pass &= pass - 1;
+        float r = raw[0];
 #pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            float x = __fmul_rn(raw[j], c.inv_temp);
-            pass |= (INCL ? x >= thr : x > thr) ? (1u << j) : 0u;
-        }
-        const int e0 = vec * VEC - c.mis;
-        while (pass) {
-            const int j = __ffs(pass) - 1;
-            pass &= pass - 1;
-            float r = raw[0];
-#pragma unroll
-            for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
-            consider<S, INCL>(buf, ctl, c, r, __fmul_rn(r, c.inv_temp), e0 + j, thr);
-        }
+        for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
+        consider<S, INCL>(buf, ctl, c, r, __fmul_rn(r, c.inv_temp), e0 + j, thr);
     }
 }
 
@@ -484,10 +530,11 @@ __device__ __forceinline__ uint32_t rank_select(Cand* buf, Ctl* ctl, int n, int 
 // otherwise.  Called by every thread with the buffer quiescent.
 template <class S>
 __device__ __forceinline__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid,
-                                                 bool* have_kth) {
+                                                 bool* have_kth, bool* ordered = nullptr) {
     __syncthreads();
     const int n = live_count(ctl);
     __syncthreads();
+    if (ordered) *ordered = n <= RANK_MAX;  // the counting select leaves its survivors in order
     if (n <= RANK_MAX) return rank_select(buf, ctl, n, k, tid, have_kth);
     return select_topk<S>(buf, ctl, hist, k, tid, have_kth);
 }
@@ -626,18 +673,141 @@ __device__ void sample_tail(const KArgs& a, int row, const MantleSampleParams& P
 
 __host__ __device__ inline size_t bitmap_words(int vocab) { return (size_t)((vocab + 31) / 32 + 2); }
 
+// The same tail for shortlists of at most 64 entries, run by one warp with the shortlist in
+// registers (lane L holds entries L and L+32): no CTA barrier, no shared-memory round trips.
+// The sums that the reference accumulates in shortlist order are accumulated in that order
+// here too -- every lane walks the same chain, fed by shuffles -- so the doubles are the
+// same doubles.  `buf` holds the n ordered survivors; sidx/sprob are scratch for the min-p
+// compaction.
+__device__ void sample_tail_warp(const KArgs& a, int row, const MantleSampleParams& P, bool greedy, int n,
+                                 const Cand* buf, int32_t* sidx, double* sprob, int lane) {
+    const unsigned full = 0xffffffffu;
+    int token, n_kept = 0, cut = 0;
+    if (n == 0) {
+        token = 0;
+    } else if (greedy) {
+        token = (int)buf[0].idx;
+    } else {
+        Cand c0, c1;
+        c0.key = c0.idx = c1.key = c1.idx = 0;
+        if (lane < n) c0 = buf[lane];
+        if (lane + 32 < n) c1 = buf[lane + 32];
+        int i0 = (int)c0.idx, i1 = (int)c1.idx;
+        const float maxv = key2f(__shfl_sync(full, c0.key, 0));
+        double p0 = lane < n ? (double)fast_exp(__fsub_rn(key2f(c0.key), maxv)) : 0.0;
+        double p1 = lane + 32 < n ? (double)fast_exp(__fsub_rn(key2f(c1.key), maxv)) : 0.0;
+        double sum = 0.0;
+        for (int i = 0; i < n; i++) sum = __dadd_rn(sum, __shfl_sync(full, i < 32 ? p0 : p1, i & 31));
+        if (sum == 0.0) {  // sampler.go:170-172
+            token = __shfl_sync(full, i0, 0);
+            n_kept = n;
+        } else {
+            const double inv = __ddiv_rn(1.0, sum);
+            p0 = __dmul_rn(p0, inv);
+            p1 = __dmul_rn(p1, inv);
+            if (P.min_p > 0.0f) {  // sampler.go:180-210
+                const double thr = __dmul_rn(__shfl_sync(full, p0, 0), (double)P.min_p);
+                const bool k0 = lane < n && p0 >= thr, k1 = lane + 32 < n && p1 >= thr;
+                const unsigned b0 = __ballot_sync(full, k0), b1 = __ballot_sync(full, k1);
+                const int m = __popc(b0) + __popc(b1);
+                double ns = 0.0;
+                for (int i = 0; i < n; i++) {
+                    const double pi = __shfl_sync(full, i < 32 ? p0 : p1, i & 31);
+                    if (((i < 32 ? b0 : b1) >> (i & 31)) & 1u) ns = __dadd_rn(ns, pi);
+                }
+                if (m < n) {
+                    const unsigned lt = (1u << lane) - 1u;
+                    if (k0) {
+                        const int q = __popc(b0 & lt);
+                        sprob[q] = p0;
+                        sidx[q] = i0;
+                    }
+                    if (k1) {
+                        const int q = __popc(b0) + __popc(b1 & lt);
+                        sprob[q] = p1;
+                        sidx[q] = i1;
+                    }
+                    __syncwarp();
+                    n = m;
+                    p0 = lane < n ? sprob[lane] : 0.0;
+                    i0 = lane < n ? sidx[lane] : 0;
+                    p1 = lane + 32 < n ? sprob[lane + 32] : 0.0;
+                    i1 = lane + 32 < n ? sidx[lane + 32] : 0;
+                    __syncwarp();
+                    if (ns > 0.0) {
+                        const double sc = __ddiv_rn(1.0, ns);
+                        p0 = __dmul_rn(p0, sc);
+                        p1 = __dmul_rn(p1, sc);
+                    }
+                }
+            }
+            n_kept = n;
+            if (n == 0) {  // min_p > 1 dropped everything: the reference indexes topIdx[-1] and panics
+                token = -1;
+                if (lane == 0 && a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_EMPTY);
+            } else {
+                // sampler.go:212-233: the nucleus prefix and the inverse-CDF walk add the same
+                // doubles in the same order, so one running sum serves both
+                double c = 0.0, c0v = 0.0, c1v = 0.0;
+                for (int i = 0; i < n; i++) {
+                    c = __dadd_rn(c, __shfl_sync(full, i < 32 ? p0 : p1, i & 31));
+                    if (i == lane) c0v = c;
+                    if (i == lane + 32) c1v = c;
+                }
+                const bool nucleus = P.top_p < 1.0f;
+                const unsigned q0 = __ballot_sync(full, nucleus && lane < n && __double2float_rn(c0v) >= P.top_p);
+                const unsigned q1 = __ballot_sync(full, nucleus && lane + 32 < n && __double2float_rn(c1v) >= P.top_p);
+                const int first = q0 ? __ffs(q0) - 1 : (q1 ? 31 + __ffs(q1) : -1);
+                cut = first < 0 ? n : first + 1;
+                const double r = P.uniform;
+                const unsigned r0 = __ballot_sync(full, lane < cut && r <= c0v);
+                const unsigned r1 = __ballot_sync(full, lane + 32 < cut && r <= c1v);
+                const int pos = r0 ? __ffs(r0) - 1 : (r1 ? 31 + __ffs(r1) : cut - 1);
+                token = __shfl_sync(full, pos < 32 ? i0 : i1, pos & 31);
+            }
+            if (a.cand_idx || a.cand_prob) {
+                const size_t base = (size_t)row * a.cand_stride;
+                if (lane < n && lane < a.cand_stride) {
+                    if (a.cand_idx) a.cand_idx[base + lane] = i0;
+                    if (a.cand_prob) a.cand_prob[base + lane] = p0;
+                }
+                if (lane + 32 < n && lane + 32 < a.cand_stride) {
+                    if (a.cand_idx) a.cand_idx[base + lane + 32] = i1;
+                    if (a.cand_prob) a.cand_prob[base + lane + 32] = p1;
+                }
+            }
+        }
+    }
+    if (lane == 0) {
+        a.next[row] = token;
+        if (a.n_kept) a.n_kept[row] = n_kept;
+        if (a.cut) a.cut[row] = cut;
+    }
+}
+
 // After the select: order the survivors and either finish the row or publish the local
 // shortlist.  The ordered arrays live in the part of the candidate buffer the survivors
-// (at most KCAP entries) do not occupy.
+// (at most KCAP entries) do not occupy.  `ordered`: the select already left them in order.
 template <class S, int MODE>
 __device__ void finish_row(const KArgs& a, int row, int split, const MantleSampleParams& P, bool greedy,
-                           Cand* buf, Ctl* ctl, int tid) {
+                           bool ordered, Cand* buf, Ctl* ctl, int tid) {
     constexpr int KC = S::KCAP;
     const int n = min(ctl->cnt, KC);
     float* sval = reinterpret_cast<float*>(buf + KC);
     int32_t* sidx = reinterpret_cast<int32_t*>(sval + KC);
     double* sprob = reinterpret_cast<double*>(sidx + KC);
-    rank_sort<S>(buf, n, sval, sidx, tid);
+    if (MODE == MODE_FUSED && ordered && n <= 64) {
+        if (tid < 32) sample_tail_warp(a, row, P, greedy, n, buf, sidx, sprob, tid);
+        return;
+    }
+    if (ordered) {
+        for (int i = tid; i < n; i += S::NT) {
+            sval[i] = key2f(buf[i].key);
+            sidx[i] = (int32_t)buf[i].idx;
+        }
+    } else {
+        rank_sort<S>(buf, n, sval, sidx, tid);
+    }
     __syncthreads();
     if (MODE == MODE_FUSED) {
         sample_tail<S>(a, row, P, greedy, n, sval, sidx, sprob, ctl, tid);
@@ -664,302 +834,583 @@ __device__ __forceinline__ MantleSampleParams row_params(const KArgs& a, int row
 }
 
 // ---------------------------------------------------------------------------------------
-// The streaming kernel.
+// Asynchronous bulk copies (TMA, untiled form) and the mbarriers that track them.
+// Both addresses are 16-byte aligned and sizes are multiples of 16 bytes by construction:
+// copies move whole 16-byte vectors from the row rounded down to a 16-byte boundary.
 
-template <class S, typename T, int MODE>
-__global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_kernel(const KArgs a) {
-    constexpr int VEC = Elem<T>::VEC;
-    constexpr int NT = S::NT, NWARP = S::NWARP, U = S::U, CAP = S::CAP;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
-    uint32_t* hist = reinterpret_cast<uint32_t*>(buf + CAP);
-    Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
-    uint32_t* bm = reinterpret_cast<uint32_t*>(smem_raw + S::SMEM_FIXED);
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int row = blockIdx.x / a.splits;
-    const int split = blockIdx.x - row * a.splits;
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
 
-    // ---- the row's parameters --------------------------------------------------------
-    const MantleSampleParams P = row_params(a, row);
-    // sampler.go:140: greedy, or the top-1 / top_p >= 1 / temperature == 1 shortcut
-    const bool greedy = P.greedy != 0 || (P.top_k == 1 && P.top_p >= 1.0f && P.temperature == 1.0f);
-    int k = greedy ? 1 : min(P.top_k, a.vocab_total);  // sampler.go:147
-    bool bad_k = false;
-    if (!greedy && (k > a.max_top_k || k > S::KCAP || k < 1)) {
-        bad_k = true;
-        k = max(1, min(min(k, a.max_top_k), S::KCAP));
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+constexpr uint32_t WAIT_HINT_NS = 20000;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+// One poll.  The suspend-time hint lets the hardware park the thread until the phase completes
+// (or the hint, in nanoseconds, runs out) instead of spinning through issue slots that the
+// other CTA on the SM could use.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Every wait on a copy is bounded by wall time: after WAIT_LIMIT_NS without the phase
+// completing the caller gives up, raises MANTLE_SAMPLE_STATUS_TIMEOUT and leaves the kernel
+// in an orderly way.  A copy normally lands within a microsecond or two.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
     }
+}
 
-    RowCtx c;
-    c.row = reinterpret_cast<const T*>(a.logits) + (size_t)row * (size_t)a.row_stride;
-    c.mis = (int)((reinterpret_cast<uintptr_t>(c.row) & 15u) / sizeof(T));
-    c.V = a.vocab;
-    c.voff = a.vocab_offset;
-    c.inv_temp = greedy ? 1.0f : __fdiv_rn(1.0f, P.temperature);  // sampler.go:144-145
-    c.pen = P.repeat_penalty;
-    c.bm = bm;
-    c.pen_bitmap = false;
-    const uint4* vbase = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(c.row) -
-                                                        (size_t)c.mis * sizeof(T));
-    const int nvec = (c.mis + c.V + VEC - 1) / VEC;
+__device__ __forceinline__ uint64_t evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
 
-    // This CTA's share of the row, in vectors and in columns.  Vectors [a0, b0) of the share
-    // lie wholly inside the row and are streamed; the columns of the (at most two) partial
-    // vectors at the row's ends are taken one by one afterwards.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
+
+// Small asynchronous copies (8 or 4 bytes) for the next item's parameters.
+__device__ __forceinline__ void cp_async8(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------
+// The repeat penalty (sampler.go:99-138): the bitmap of the de-duplicated history window.
+
+// The history window of one row and how it reaches the CTA.
+struct WinPlan {
+    bool active;  // the penalty runs on this row (sampler.go:99)
+    bool staged;  // the window is copied to shared memory ahead of time
+    int start;    // window = ids [start, hl) of the row's history (sampler.go:100-101)
+    int a4, n4;   // 16-byte aligned superset [a4, a4 + n4) that the copy moves
+};
+
+__device__ __forceinline__ WinPlan win_plan(const KArgs& a, const MantleSampleParams& P, int hl) {
+    WinPlan w;
+    w.active = P.repeat_penalty > 1.0f && hl > 0;
+    w.start = max(hl - P.repeat_last_n, 0);
+    w.a4 = w.start & ~3;
+    w.n4 = min((hl + 3) & ~3, a.hist_stride) - w.a4;
+    w.staged = w.active && a.hist_tma_ok && w.n4 > 0 && w.n4 <= HIST_CAP;
+    return w;
+}
+
+__device__ void build_penalty_bitmap(const KArgs& a, int row, const WinPlan& w, int hl, const int32_t* win, int V,
+                                     int voff, uint32_t* bm, int tid, int nt) {
+    const int nwords = (int)bitmap_words(V);
+    for (int i = tid; i < nwords; i += nt) bm[i] = 0;
+    __syncthreads();
+    const int32_t* h = w.staged ? win - w.a4 : a.history + (size_t)row * (size_t)a.hist_stride;
+    for (int j = w.start + tid; j < hl; j += nt) {
+        int id = h[j];
+        if (id >= 0 && id < a.vocab_total) {  // sampler.go:116
+            id -= voff;
+            if (id >= 0 && id < V) atomicOr(&bm[id >> 5], 1u << (id & 31));
+        }
+    }
+    __syncthreads();
+    for (int j = tid; j < a.n_exclude; j += nt) {  // sampler.go:122-126
+        int id = a.exclude[j];
+        if (id >= 0 && id < a.vocab_total) {
+            id -= voff;
+            if (id >= 0 && id < V) atomicAnd(&bm[id >> 5], ~(1u << (id & 31)));
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int history_len(const KArgs& a, int row) {
+    if (!a.history || (a.flags & MANTLE_SAMPLE_PENALTY_PREAPPLIED)) return 0;
+    int hl = a.hist_len ? a.hist_len[row] : a.hist_stride;
+    return max(0, min(hl, a.hist_stride));
+}
+
+// The penalty alone, in place: one CTA per row rewrites each flagged logit once.
+constexpr int PENALTY_NT = 512;
+
+__global__ void __launch_bounds__(PENALTY_NT) penalty_rows_kernel(const KArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint32_t* bm = reinterpret_cast<uint32_t*>(smem_raw);
+    const int tid = threadIdx.x;
+    const int row = blockIdx.x;
+    const MantleSampleParams P = row_params(a, row);
+    const int hl = history_len(a, row);
+    WinPlan w = win_plan(a, P, hl);
+    if (!w.active) return;
+    w.staged = false;
+    build_penalty_bitmap(a, row, w, hl, nullptr, a.vocab, a.vocab_offset, bm, tid, PENALTY_NT);
+    float* wrow = const_cast<float*>(reinterpret_cast<const float*>(a.logits)) + (size_t)row * (size_t)a.row_stride;
+    const int nwords = (int)bitmap_words(a.vocab);
+    for (int i = tid; i < nwords; i += PENALTY_NT) {
+        uint32_t bits = bm[i];
+        while (bits) {
+            int b = __ffs(bits) - 1;
+            bits &= bits - 1;
+            int e = i * 32 + b;
+            wrow[e] = penalise(wrow[e], P.repeat_penalty);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// The streaming kernel: persistent CTAs, rows fed through a ring of shared-memory stages
+// by asynchronous bulk copies.
+//
+// A CTA owns work items (row, split) blockIdx.x, blockIdx.x + gridDim.x, ...  The complete
+// 16-byte vectors of an item are cut into chunks of NT*U vectors; thread 0 keeps `stages`
+// chunks in flight or landed at all times, in item order, running ahead across item
+// boundaries -- so the copies of the next row proceed while the current row's shortlist
+// is cut, ordered and sampled.  All threads consume a chunk from shared memory, meet at
+// one barrier (which also carries the "buffer needs a cut" vote), and thread 0 refills
+// the stage just freed.  Thread 0 also looks one item ahead: the next item's parameters,
+// history length and history window are in shared memory before the item starts.
+
+template <typename T, class S>
+struct ItemGeom {
+    const uint4* vbase;  // the row rounded down to 16 bytes
+    const void* row;
+    int mis;       // elements between vbase and the row pointer
+    int a0, b0;    // complete vectors [a0, b0) of this item
+    int elo, ehi;  // columns [elo, ehi) of this item
+    int nchunks;
+};
+
+template <typename T, class S>
+__device__ __forceinline__ ItemGeom<T, S> item_geom(const KArgs& a, int item) {
+    constexpr int VEC = Elem<T>::VEC;
+    constexpr int CV = S::NT * S::U;
+    ItemGeom<T, S> g;
+    const int row = item / a.splits;
+    const int split = item - row * a.splits;
+    g.row = reinterpret_cast<const T*>(a.logits) + (size_t)row * (size_t)a.row_stride;
+    g.mis = (int)((reinterpret_cast<uintptr_t>(g.row) & 15u) / sizeof(T));
+    g.vbase = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(g.row) - (size_t)g.mis * sizeof(T));
+    const int nvec = (g.mis + a.vocab + VEC - 1) / VEC;
     const int per = (nvec + a.splits - 1) / a.splits;
     const int vlo = min(split * per, nvec);
     const int vhi = min(vlo + per, nvec);
-    const int elo = max(vlo * VEC - c.mis, 0);
-    const int ehi = min(vhi * VEC - c.mis, c.V);
-    constexpr int RV = NT * U;  // vectors per region
-    const int a0 = max(vlo, c.mis != 0 ? 1 : 0);
-    const int b0 = min(vhi, (c.mis + c.V) / VEC);
-    const int nreg = b0 > a0 ? (b0 - a0 + RV - 1) / RV : 0;
+    g.elo = max(vlo * VEC - g.mis, 0);
+    g.ehi = min(vhi * VEC - g.mis, a.vocab);
+    g.a0 = max(vlo, g.mis != 0 ? 1 : 0);
+    g.b0 = min(vhi, (g.mis + a.vocab) / VEC);
+    g.nchunks = g.b0 > g.a0 ? (g.b0 - g.a0 + CV - 1) / CV : 0;
+    return g;
+}
 
-    int hl = 0;
-    if (a.history && !(a.flags & MANTLE_SAMPLE_PENALTY_PREAPPLIED)) {
-        hl = a.hist_len ? a.hist_len[row] : a.hist_stride;
-        hl = max(0, min(hl, a.hist_stride));
+// The effective shortlist length of a row and whether it takes the argmax shortcut.
+__device__ __forceinline__ int row_k(const KArgs& a, const MantleSampleParams& P, int kcap, bool* greedy, bool* bad) {
+    // sampler.go:140: greedy, or the top-1 / top_p >= 1 / temperature == 1 shortcut
+    *greedy = P.greedy != 0 || (P.top_k == 1 && P.top_p >= 1.0f && P.temperature == 1.0f);
+    int k = *greedy ? 1 : min(P.top_k, a.vocab_total);  // sampler.go:147
+    *bad = false;
+    if (!*greedy && (k > a.max_top_k || k > kcap || k < 1)) {
+        *bad = true;
+        k = max(1, min(min(k, a.max_top_k), kcap));
     }
-    const bool pen_active = P.repeat_penalty > 1.0f && hl > 0;
-    const bool in_place = MODE == MODE_PENALTY || (a.flags & MANTLE_SAMPLE_WRITE_BACK_PENALTY) != 0;
-    bool careful = k > 32 * NWARP;
+    return k;
+}
 
-    // The first region's loads go out before anything else, so that they are in flight while
-    // the bitmap is built -- unless the penalty is about to rewrite the row in place.
-    uint4 ra[U], rb[U];
-    const bool early = MODE != MODE_PENALTY && !careful && nreg > 0 && !(pen_active && in_place);
-    if (early) {
+template <class S, typename T, int MODE>
+__global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_kernel(const KArgs a, const int stages) {
+    constexpr int VEC = Elem<T>::VEC;
+    constexpr int NT = S::NT, NWARP = S::NWARP, U = S::U, CAP = S::CAP;
+    constexpr int CV = NT * U;                 // vectors per chunk
+    constexpr uint32_t CHUNK_BYTES = CV * 16;  // bytes per stage
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(buf + CAP);
+    Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
+    Pre* pre = reinterpret_cast<Pre*>(reinterpret_cast<unsigned char*>(ctl) + 512);
+    int32_t* win = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(pre) + 256);
+    unsigned char* ring = smem_raw + S::SMEM_FIXED;
+    uint32_t* bm = reinterpret_cast<uint32_t*>(ring + (size_t)stages * CHUNK_BYTES);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nitems = a.rows * a.splits;
+
+    if (tid == 0) {
+        for (int s = 0; s < stages; s++) mbar_init(&ctl->full[s], 1);
+        mbar_init(&pre->win_full, 1);
+        ctl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // ---- look-ahead (thread 0): the next item's parameters, history length and window -------
+    const bool per_row_len = a.history != nullptr && a.hist_len != nullptr &&
+                             !(a.flags & MANTLE_SAMPLE_PENALTY_PREAPPLIED);
+    auto item_hl = [&](int slot) {  // history length of the item whose look-ahead sits in `slot`
+        if (!a.history || (a.flags & MANTLE_SAMPLE_PENALTY_PREAPPLIED)) return 0;
+        const int hl = a.hist_len ? pre->hl[slot] : a.hist_stride;
+        return max(0, min(hl, a.hist_stride));
+    };
+    auto fetch_params = [&](int item, int slot) {  // asynchronous; completed by cp_async_wait_all
+        const int r = item / a.splits;
+        if (a.params) {
+            const char* src = reinterpret_cast<const char*>(a.params + r);
+            char* dst = reinterpret_cast<char*>(&pre->p[slot]);
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            int v = a0 + u * NT + tid;
-            ra[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+            for (int q = 0; q < (int)sizeof(MantleSampleParams); q += 8) cp_async8(dst + q, src + q);
+        }
+        if (per_row_len) cp_async4(&pre->hl[slot], a.hist_len + r);
+        cp_async_commit();
+    };
+    auto slot_params = [&](int slot) {
+        if (a.params) return pre->p[slot];
+        return row_params(a, 0);  // plain argmax rows
+    };
+    auto fetch_window = [&](int item, int slot) {  // needs the slot's parameters to have landed
+        const MantleSampleParams Pn = slot_params(slot);
+        const WinPlan w = win_plan(a, Pn, item_hl(slot));
+        if (w.staged) {
+            pre->w_issued++;
+            const int32_t* src = a.history + (size_t)(item / a.splits) * (size_t)a.hist_stride + w.a4;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&pre->win_full, (uint32_t)w.n4 * 4u);
+            bulk_load(win, src, (uint32_t)w.n4 * 4u, &pre->win_full, pre->pol);
+        }
+    };
+
+    // ---- producer (thread 0; its state lives in `pre`) ---------------------------------------
+    // items whose shortlist is too long for the seeded threshold stream nothing: they go
+    // straight to the careful path
+    auto fast_item = [&](int item) {
+        if (a.max_top_k <= 32 * NWARP) return true;  // no row can exceed the bound: nothing to look up
+        bool greedy, bad;
+        const MantleSampleParams Pq = row_params(a, item / a.splits);
+        return row_k(a, Pq, S::KCAP, &greedy, &bad) <= 32 * NWARP;
+    };
+    auto producer_open = [&]() {  // geometry of item pre->p_item
+        pre->p_chunk = 0;
+        pre->p_nchunks = 0;
+        if (pre->p_item < nitems) {
+            const ItemGeom<T, S> g = item_geom<T, S>(a, pre->p_item);
+            pre->p_vbase = g.vbase;
+            pre->p_a0 = g.a0;
+            pre->p_b0 = g.b0;
+            pre->p_nchunks = fast_item(pre->p_item) ? g.nchunks : 0;
+        }
+    };
+    auto issue_next = [&]() {  // thread 0: the next chunk in item order, if any is left
+        while (pre->p_item < nitems) {
+            const int pc = pre->p_chunk;
+            if (pc < pre->p_nchunks) {
+                const int v = pre->p_a0 + pc * CV;
+                const uint32_t bytes = (uint32_t)min(CV, pre->p_b0 - v) * 16u;
+                const uint32_t s = pre->g_issued % (uint32_t)stages;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(&ctl->full[s], bytes);
+                bulk_load(ring + (size_t)s * CHUNK_BYTES, pre->p_vbase + v, bytes, &ctl->full[s], pre->pol);
+                pre->p_chunk = pc + 1;
+                pre->g_issued++;
+                return;
+            }
+            pre->p_item += gridDim.x;
+            producer_open();
+        }
+    };
+    if (tid == 0) {
+        pre->pol = evict_first_policy();
+        pre->p_item = blockIdx.x;
+        pre->g_issued = 0;
+        pre->w_issued = 0;
+        producer_open();
+        for (int s = 0; s < stages; s++) issue_next();
+        if ((int)blockIdx.x < nitems) {
+            fetch_params(blockIdx.x, 0);
+            cp_async_wait_all();
+            fetch_window(blockIdx.x, 0);
         }
     }
-    if (tid == 0) ctl->cnt = 0;
 
-    // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
-    if (pen_active) {
-        const int nwords = (int)bitmap_words(c.V);
-        for (int w = tid; w < nwords; w += NT) bm[w] = 0;
-        __syncthreads();
-        const int start = max(hl - P.repeat_last_n, 0);
-        const int32_t* h = a.history + (size_t)row * (size_t)a.hist_stride;
-        for (int j = start + tid; j < hl; j += NT) {
-            int id = h[j];
-            if (id >= 0 && id < a.vocab_total) {  // sampler.go:116
-                id -= c.voff;
-                if (id >= 0 && id < c.V) atomicOr(&bm[id >> 5], 1u << (id & 31));
-            }
+    uint32_t g_done = 0;  // chunks consumed so far (same in every thread)
+    uint32_t w_done = 0;  // staged windows consumed so far (same in every thread)
+    int it_index = 0;
+    bool aborted = false;
+
+    for (int item = blockIdx.x; item < nitems && !aborted; item += gridDim.x, it_index++) {
+        const int row = item / a.splits;
+        const int split = item - row * a.splits;
+        const int slot = it_index & 1;
+        const int next_item = item + gridDim.x;
+
+        __syncthreads();  // the previous item is done with buffer and bitmap; the look-ahead is visible
+        if (tid == 0) ctl->cnt = 0;
+        const MantleSampleParams P = slot_params(slot);
+        const int hl = item_hl(slot);
+        bool greedy, bad_k;
+        const int k = row_k(a, P, S::KCAP, &greedy, &bad_k);
+        const ItemGeom<T, S> g = item_geom<T, S>(a, item);
+        if (tid == 0 && next_item < nitems) fetch_params(next_item, slot ^ 1);
+        bool looked_ahead = false;  // thread 0: the next item's window has been requested
+
+        RowCtx c;
+        c.row = g.row;
+        c.mis = g.mis;
+        c.V = a.vocab;
+        c.voff = a.vocab_offset;
+        c.inv_temp = greedy ? 1.0f : __fdiv_rn(1.0f, P.temperature);  // sampler.go:144-145
+        c.pen = P.repeat_penalty;
+        c.bm = bm;
+        c.pen_bitmap = false;
+        const int a0 = g.a0, b0 = g.b0, elo = g.elo, ehi = g.ehi;
+        bool careful = k > 32 * NWARP;
+        const int nchunks = careful ? 0 : g.nchunks;
+
+        // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
+        const WinPlan wp = win_plan(a, P, hl);
+        if (wp.staged) {
+            if (!mbar_wait(&pre->win_full, w_done & 1u)) ctl->abort = 1;
+            w_done++;
+        }
+        if (wp.active && !DEBUG_OFF(a, 0)) {
+            build_penalty_bitmap(a, row, wp, hl, win, c.V, c.voff, bm, tid, NT);
+            c.pen_bitmap = true;
         }
         __syncthreads();
-        for (int j = tid; j < a.n_exclude; j += NT) {  // sampler.go:122-126
-            int id = a.exclude[j];
-            if (id >= 0 && id < a.vocab_total) {
-                id -= c.voff;
-                if (id >= 0 && id < c.V) atomicAnd(&bm[id >> 5], ~(1u << (id & 31)));
-            }
-        }
-        __syncthreads();
-        if (in_place) {
-            // the reference's in-place form: one read-modify-write per distinct id this CTA owns
-            if (sizeof(T) == 4) {
-                float* wrow = const_cast<float*>(reinterpret_cast<const float*>(c.row));
-                for (int w = tid; w < nwords; w += NT) {
-                    uint32_t bits = bm[w];
-                    while (bits) {
-                        int b = __ffs(bits) - 1;
-                        bits &= bits - 1;
-                        int e = w * 32 + b;
-                        if (e >= elo && e < ehi) wrow[e] = penalise(wrow[e], c.pen);
+
+        // ---- stream the item's chunks -------------------------------------------------------
+        const int trig = min(k + max(k >> 1, 16), CAP / 2);  // cut the buffer at this many entries
+        float thr = __uint_as_float(0xff800000u);            // -inf
+
+        for (int cc = 0; cc < nchunks; cc++, g_done++) {
+            const uint32_t s = g_done % (uint32_t)stages;
+            const uint32_t parity = (g_done / (uint32_t)stages) & 1u;
+            bool landed = mbar_wait(&ctl->full[s], parity);
+            if (!landed) ctl->abort = 1;
+            // the first chunk's filter meets at a barrier of its own: enter it all together or not at all
+            if (cc == 0 && !careful) landed = __syncthreads_and(landed);
+            const uint4* stage = reinterpret_cast<const uint4*>(ring + (size_t)s * CHUNK_BYTES);
+            const int v0 = a0 + cc * CV + tid;  // this thread's first vector of the chunk
+            if (landed && !careful) {
+                if (cc == 0) {
+                    // A threshold that at least k columns of this chunk reach: with
+                    // j = ceil(k / warps), every warp holds j thread-maxima >= its j-th largest
+                    // one, so the smallest of those per-warp values is reached by >= k columns.
+                    // The maxima are taken over penalised values: the bound must hold for them.
+                    float tmax = __uint_as_float(0xff800000u);
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+                        if (v0 + u * NT < b0)
+                            tmax = fmaxf(tmax, vec_max_penalised<T>(stage[u * NT + tid], v0 + u * NT, c));
+                    float x = tmax;  // bitonic sort across the warp, descending
+#pragma unroll
+                    for (int k2 = 2; k2 <= 32; k2 <<= 1) {
+#pragma unroll
+                        for (int j2 = k2 >> 1; j2 > 0; j2 >>= 1) {
+                            float y = __shfl_xor_sync(0xffffffffu, x, j2);
+                            bool desc = (lane & k2) == 0;
+                            bool lower = (lane & j2) == 0;
+                            x = (lower == desc) ? fmaxf(x, y) : fminf(x, y);
+                        }
+                    }
+                    const int j = (k + NWARP - 1) / NWARP;
+                    float wj = __shfl_sync(0xffffffffu, x, j - 1);
+                    if (lane == 0) ctl->warpv[warp] = wj;
+                    __syncthreads();
+                    float t0 = ctl->warpv[0];
+#pragma unroll
+                    for (int w = 1; w < NWARP; w++) t0 = fminf(t0, ctl->warpv[w]);
+                    thr = t0;
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+                        if (v0 + u * NT < b0)
+                            filter_vec<S, T, true>(stage[u * NT + tid], v0 + u * NT, c, thr, buf, ctl);
+                } else {
+                    // Later columns: the buffer already holds k entries >= thr with lower
+                    // indices, so an equal value can no longer enter (sampler.go:268-275).
+                    // One test per thread and chunk in the common case: the largest of its
+                    // U * VEC scaled values against the threshold.
+                    const bool whole = cc + 1 < nchunks;  // only the last chunk can be partial
+                    uint4 rv[U];
+                    float m = __uint_as_float(0xff800000u);
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        if (whole || v0 + u * NT < b0) {
+                            rv[u] = stage[u * NT + tid];
+                            m = fmaxf(m, vec_max_scaled<T>(rv[u], c.inv_temp));
+                        }
+                    }
+                    if (m > thr) {
+#pragma unroll
+                        for (int u = 0; u < U; u++)
+                            if (whole || v0 + u * NT < b0)
+                                filter_vec<S, T, false>(rv[u], v0 + u * NT, c, thr, buf, ctl);
                     }
                 }
             }
-        } else {
-            c.pen_bitmap = true;
-        }
-    }
-    if (MODE == MODE_PENALTY) return;
-    __syncthreads();
-
-    // ---- stream the row ------------------------------------------------------------------
-    const int trig = min(k + max(k >> 1, 16), CAP / 2);  // refresh the threshold at this many entries
-    float thr = __uint_as_float(0xff800000u);            // -inf
-
-    if (!careful && nreg > 0) {
-        if (!early) {
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                int v = a0 + u * NT + tid;
-                ra[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+            // One barrier per chunk.  The thread that made the last append of the chunk reads
+            // the final count before it arrives, so the OR is the same for every thread.
+            int lim = cc == 0 ? k + 1 : trig;
+            if (DEBUG_OFF(a, 3)) lim = CAP + 1;
+            if (DEBUG_OFF(a, 2)) thr = __uint_as_float(0x7f800000u);
+            const bool vote = __syncthreads_or(live_count(ctl) >= lim || !landed);
+            if (tid == 0) {
+                issue_next();  // the stage is free again
+                if (!looked_ahead && next_item < nitems) {
+                    // by now the next item's parameters have long landed, and this item is done
+                    // with the window buffer: request the next window
+                    cp_async_wait_all();
+                    fetch_window(next_item, slot ^ 1);
+                    looked_ahead = true;
+                }
+            }
+            if (vote) {
+                if (*reinterpret_cast<volatile int*>(&ctl->abort)) {
+                    aborted = true;
+                    g_done++;
+                    break;
+                }
+                if (!careful) {
+                    if (live_count(ctl) > CAP) {
+                        careful = true;  // entries were dropped: redo the item on the careful path
+                    } else {
+                        bool have;
+                        uint32_t kth = refresh_topk<S>(buf, ctl, hist, k, tid, &have);
+                        if (have) thr = key2f(kth);
+                    }
+                }
             }
         }
-        // `load(dst, r)`: region r into dst (predicated: only the last region can be partial)
-        auto load = [&](uint4(&dst)[U], int r) {
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                int v = a0 + r * RV + u * NT + tid;
-                dst[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+        if (aborted) break;
+
+        if (!careful) {
+            // the columns of the partial vectors at the ends of this item
+            int r1_lo = elo, r1_hi = ehi, r2_lo = ehi, r2_hi = ehi;
+            if (b0 > a0) {
+                r1_hi = min(ehi, max(elo, a0 * VEC - c.mis));
+                r2_lo = max(elo, b0 * VEC - c.mis);
             }
-        };
-        // `later(src, r)`: regions after the first.  The buffer already holds k entries >= thr
-        // with lower indices, so an equal value can no longer enter (sampler.go:268-275).
-        auto later = [&](const uint4(&src)[U], int r) {
-            const int v0 = a0 + r * RV + tid;
-            if (r + 1 < nreg) {
-#pragma unroll
-                for (int u = 0; u < U; u++) filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
-            } else {
-#pragma unroll
-                for (int u = 0; u < U; u++)
-                    if (v0 + u * NT < b0) filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
+            const int n1 = r1_hi - r1_lo, n2 = r2_hi - r2_lo;
+            if (tid < n1 + n2) {  // at most 4 * VEC columns
+                int e = tid < n1 ? r1_lo + tid : r2_lo + (tid - n1);
+                float raw = Elem<T>::load1(c.row, e);
+                float v = __fmul_rn(raw, c.inv_temp);
+                if (v >= thr) consider<S, true>(buf, ctl, c, raw, v, e, thr);
             }
-        };
-        // One barrier per region.  The thread that made the last append of the region reads
-        // the final count before it arrives, so the OR is the same for every thread.
-        auto region_end = [&](int lim) {
-            if (__syncthreads_or(live_count(ctl) >= lim)) {
-                if (live_count(ctl) > CAP) {
-                    careful = true;  // entries were dropped: start over on the careful path
-                } else {
+            __syncthreads();
+            if (live_count(ctl) > CAP) careful = true;
+            __syncthreads();
+        }
+
+        if (careful) {
+            // Careful path: any input, any order, plain loads.  Steps of NT*SLOW_EPT columns
+            // with room for a whole step guaranteed before it starts; the buffer is cut to k
+            // whenever it could overflow.  Reached for k beyond 32 per warp, for rows whose
+            // first chunk ties massively, and for adversarial orders (e.g. ascending logits).
+            __syncthreads();
+            if (tid == 0) ctl->cnt = 0;
+            __syncthreads();
+            thr = __uint_as_float(0xff800000u);
+            bool strict = false;
+            constexpr int STEP = NT * S::SLOW_EPT;
+            for (int e0 = elo; e0 < ehi; e0 += STEP) {
+                __syncthreads();
+                if (ctl->cnt + STEP > CAP) {
                     bool have;
-                    uint32_t kth = refresh_topk<S>(buf, ctl, hist, k, tid, &have);
-                    if (have) thr = key2f(kth);
+                    uint32_t kth = select_topk<S>(buf, ctl, hist, k, tid, &have);
+                    if (have) {
+                        thr = key2f(kth);
+                        strict = true;
+                    }
                 }
-            }
-        };
-
-        // -- region 0 --
-        if (nreg > 1) load(rb, 1);
-        {
-            // A threshold that at least k columns of this region reach: with
-            // j = ceil(k / warps), every warp holds j thread-maxima >= its j-th largest one,
-            // so the smallest of those per-warp values is reached by >= k columns.
-            const int v0 = a0 + tid;
-            float tmax = __uint_as_float(0xff800000u);
+                __syncthreads();
 #pragma unroll
-            for (int u = 0; u < U; u++)
-                if (v0 + u * NT < b0) tmax = fmaxf(tmax, vec_max_penalised<T>(ra[u], v0 + u * NT, c));
-            float x = tmax;  // bitonic sort across the warp, descending
-#pragma unroll
-            for (int k2 = 2; k2 <= 32; k2 <<= 1) {
-#pragma unroll
-                for (int j2 = k2 >> 1; j2 > 0; j2 >>= 1) {
-                    float y = __shfl_xor_sync(0xffffffffu, x, j2);
-                    bool desc = (lane & k2) == 0;
-                    bool lower = (lane & j2) == 0;
-                    x = (lower == desc) ? fmaxf(x, y) : fminf(x, y);
-                }
-            }
-            const int j = (k + NWARP - 1) / NWARP;
-            float wj = __shfl_sync(0xffffffffu, x, j - 1);
-            if (lane == 0) ctl->warpv[warp] = wj;
-            __syncthreads();
-            float t0 = ctl->warpv[0];
-#pragma unroll
-            for (int w = 1; w < NWARP; w++) t0 = fminf(t0, ctl->warpv[w]);
-            thr = t0;
-#pragma unroll
-            for (int u = 0; u < U; u++)
-                if (v0 + u * NT < b0) filter_vec<S, T, true>(ra[u], v0 + u * NT, c, thr, buf, ctl);
-        }
-        region_end(k + 1);
-
-        // -- regions 1.. : two register sets, each refilled while the other is filtered --
-        int r = 1;
-        while (r < nreg && !careful) {
-            if (r + 1 < nreg) load(ra, r + 1);
-            later(rb, r);
-            region_end(trig);
-            if (++r >= nreg || careful) break;
-            if (r + 1 < nreg) load(rb, r + 1);
-            later(ra, r);
-            region_end(trig);
-            ++r;
-        }
-    }
-
-    if (!careful) {
-        // the columns of the partial vectors at the ends of this CTA's share
-        int r1_lo = elo, r1_hi = ehi, r2_lo = ehi, r2_hi = ehi;
-        if (b0 > a0) {
-            r1_hi = min(ehi, max(elo, a0 * VEC - c.mis));
-            r2_lo = max(elo, b0 * VEC - c.mis);
-        }
-        const int n1 = r1_hi - r1_lo, n2 = r2_hi - r2_lo;
-        if (tid < n1 + n2) {  // at most 4 * VEC columns
-            int e = tid < n1 ? r1_lo + tid : r2_lo + (tid - n1);
-            float raw = Elem<T>::load1(c.row, e);
-            float v = __fmul_rn(raw, c.inv_temp);
-            if (v >= thr) consider<S, true>(buf, ctl, c, raw, v, e, thr);
-        }
-        __syncthreads();
-        if (live_count(ctl) > CAP) careful = true;
-        __syncthreads();
-    }
-
-    if (careful) {
-        // Careful path: any input, any order.  Steps of NT*SLOW_EPT columns with room for a
-        // whole step guaranteed before it starts; the buffer is cut to k whenever it could
-        // overflow.  Reached for k beyond 32 per warp, for rows whose first region ties
-        // massively, and for adversarial orders (e.g. ascending logits).
-        __syncthreads();
-        if (tid == 0) ctl->cnt = 0;
-        __syncthreads();
-        thr = __uint_as_float(0xff800000u);
-        bool strict = false;
-        constexpr int STEP = NT * SLOW_EPT;
-        for (int e0 = elo; e0 < ehi; e0 += STEP) {
-            __syncthreads();
-            if (ctl->cnt + STEP > CAP) {
-                bool have;
-                uint32_t kth = select_topk<S>(buf, ctl, hist, k, tid, &have);
-                if (have) {
-                    thr = key2f(kth);
-                    strict = true;
+                for (int j = 0; j < S::SLOW_EPT; j++) {
+                    int e = e0 + j * NT + tid;
+                    if (e < ehi) {
+                        float l = Elem<T>::load1(c.row, e);
+                        if (c.pen_bitmap && bm_test(bm, e)) l = penalise(l, c.pen);
+                        float v = __fmul_rn(l, c.inv_temp);
+                        if (strict ? (v > thr) : (v >= thr)) append<S>(buf, ctl, v, e + c.voff);
+                    }
                 }
             }
             __syncthreads();
-#pragma unroll
-            for (int j = 0; j < SLOW_EPT; j++) {
-                int e = e0 + j * NT + tid;
-                if (e < ehi) {
-                    float l = Elem<T>::load1(c.row, e);
-                    if (c.pen_bitmap && bm_test(bm, e)) l = penalise(l, c.pen);
-                    float v = __fmul_rn(l, c.inv_temp);
-                    if (strict ? (v > thr) : (v >= thr)) append<S>(buf, ctl, v, e + c.voff);
+        }
+
+        // ---- cut to k, order, finish --------------------------------------------------------
+        bool have, ordered;
+        refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
+        __syncthreads();
+        if (bad_k) {
+            if (tid == 0) {
+                if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_TOPK_RANGE);
+                if (MODE == MODE_FUSED) {
+                    a.next[row] = -1;
+                    if (a.n_kept) a.n_kept[row] = 0;
+                    if (a.cut) a.cut[row] = 0;
+                } else {
+                    a.part_cnt[(size_t)split * a.rows + row] = 0;
                 }
             }
+        } else if (!DEBUG_OFF(a, 1)) {
+            finish_row<S, MODE>(a, row, split, P, greedy, ordered, buf, ctl, tid);
         }
-        __syncthreads();
+        if (tid == 0 && !looked_ahead && next_item < nitems) {  // items that streamed no chunk
+            cp_async_wait_all();
+            fetch_window(next_item, slot ^ 1);
+        }
     }
 
-    // ---- cut to k, order, finish ------------------------------------------------------------
-    bool have;
-    refresh_topk<S>(buf, ctl, hist, k, tid, &have);
-    __syncthreads();
-    if (bad_k) {
+    if (aborted) {
+        // A copy never landed.  Report it, give the copies still in flight a bounded time to
+        // land (their destination is this CTA's shared memory), and leave.
         if (tid == 0) {
-            if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_TOPK_RANGE);
-            if (MODE == MODE_FUSED) {
-                a.next[row] = -1;
-                if (a.n_kept) a.n_kept[row] = 0;
-                if (a.cut) a.cut[row] = 0;
-            } else {
-                a.part_cnt[(size_t)split * a.rows + row] = 0;
-            }
+            if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_TIMEOUT);
+            for (uint32_t q = g_done; q < pre->g_issued; q++)
+                mbar_wait(&ctl->full[q % (uint32_t)stages], (q / (uint32_t)stages) & 1u);
+            cp_async_wait_all();
+            if (pre->w_issued > w_done) mbar_wait(&pre->win_full, w_done & 1u);
         }
-        return;
+        __syncthreads();
+    } else if (tid == 0 && ctl->abort && a.status) {
+        atomicOr(a.status, MANTLE_SAMPLE_STATUS_TIMEOUT);  // a history window never landed
     }
-    finish_row<S, MODE>(a, row, split, P, greedy, buf, ctl, tid);
 }
 
 // Merge of `parts` local shortlists per row (several CTAs of one GPU, or one per
 // vocabulary shard after an all-gather), then the tail.
 __global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_parts_kernel(const KArgs a) {
     using S = ShapeLargeK;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     Cand* buf = reinterpret_cast<Cand*>(smem_raw);
     uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
     Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
@@ -988,23 +1439,16 @@ __global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_part
         }
         return;
     }
-    bool have;
-    refresh_topk<S>(buf, ctl, hist, k, tid, &have);
+    bool have, ordered;
+    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
     __syncthreads();
-    finish_row<S, MODE_FUSED>(a, row, 0, P, greedy, buf, ctl, tid);
+    finish_row<S, MODE_FUSED>(a, row, 0, P, greedy, ordered, buf, ctl, tid);
 }
 
 // ---------------------------------------------------------------------------------------
 // host side
 
 constexpr int kInvalid = (int)cudaErrorInvalidValue;
-
-int sm_count() {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
-    return n;
-}
 
 bool batch_ok(const MantleSampleBatch* b, bool need_outputs) {
     if (!b || !b->logits || b->rows <= 0 || b->vocab <= 0) return false;
@@ -1018,6 +1462,7 @@ bool batch_ok(const MantleSampleBatch* b, bool need_outputs) {
     if ((b->flags & MANTLE_SAMPLE_WRITE_BACK_PENALTY) && b->dtype != MANTLE_DTYPE_F32) return false;
     const size_t esz = b->dtype == MANTLE_DTYPE_F32 ? 4 : 2;
     if (reinterpret_cast<uintptr_t>(b->logits) % esz) return false;
+    if (b->params && reinterpret_cast<uintptr_t>(b->params) % 8) return false;
     if (need_outputs) {
         if (!b->params || !b->next) return false;
         if (b->max_top_k < 1 || b->max_top_k > KMAX) return false;
@@ -1028,29 +1473,72 @@ bool batch_ok(const MantleSampleBatch* b, bool need_outputs) {
 
 // Shape selection.  MANTLE_SAMPLER_SHAPE=small|large overrides it (a tuning aid: `small`
 // is refused, by falling back, for batches whose top_k it cannot serve).
-bool use_small_shape(int max_top_k) {
+int forced_shape() {
     static const int forced = [] {
         const char* e = getenv("MANTLE_SAMPLER_SHAPE");
         if (!e) return 0;
-        return strcmp(e, "small") == 0 ? 1 : (strcmp(e, "large") == 0 ? 2 : 0);
+        return strcmp(e, "small") == 0 ? 1 : (strcmp(e, "large") == 0 ? 2 : (strcmp(e, "alt") == 0 ? 3 : 0));
     }();
+    return forced;
+}
+
+bool use_small_shape(int max_top_k) {
     if (max_top_k > ShapeSmallK::KCAP) return false;
-    return forced != 2;
+    return forced_shape() != 2;
+}
+
+bool use_alt_shape(int max_top_k) { return forced_shape() == 3 && max_top_k <= ShapeAlt::KCAP; }
+
+struct SmemBudget {
+    int per_sm;     // shared memory of one SM
+    int per_block;  // largest opt-in dynamic shared memory of one CTA
+    int sms;
+};
+
+SmemBudget smem_budget() {
+    SmemBudget b = {233472, 232448, 148};  // B200 figures, used when no device can be asked
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return b;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess && v > 0) b.per_sm = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess && v > 0) b.per_block = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) b.sms = v;
+    return b;
+}
+
+// Ring depth and CTAs per SM for one shape and vocabulary: as many stages as fit beside the
+// candidate buffer and the bitmap with MINB CTAs on an SM; one CTA per SM with a deeper ring
+// when fewer than two stages would fit.
+template <class S>
+bool plan_ring(int vocab, const SmemBudget& bud, int* stages, int* ctas_per_sm, size_t* smem) {
+    const size_t chunk = (size_t)S::NT * S::U * 16;
+    const size_t fixed = S::SMEM_FIXED + bitmap_words(vocab) * sizeof(uint32_t);
+    for (int ctas = S::MINB; ctas >= 1; ctas--) {
+        const long long room = std::min<long long>(bud.per_sm / ctas - 1024, bud.per_block) - (long long)fixed;
+        int st = room > 0 ? (int)(room / (long long)chunk) : 0;
+        st = std::min(st, ctas == 1 ? 6 : 3);
+        if (st >= 2) {
+            *stages = st;
+            *ctas_per_sm = ctas;
+            *smem = fixed + (size_t)st * chunk;
+            return true;
+        }
+    }
+    return false;
 }
 
 int choose_splits(const MantleSampleBatch* b) {
     const int vec = b->dtype == MANTLE_DTYPE_F32 ? 4 : 8;
     const int nvec = (b->vocab + vec - 1) / vec + 1;
     const bool small = use_small_shape(b->max_top_k);
-    const int region = small ? ShapeSmallK::NT * ShapeSmallK::U : ShapeLargeK::NT * ShapeLargeK::U;
+    const int chunk = small ? ShapeSmallK::NT * ShapeSmallK::U : ShapeLargeK::NT * ShapeLargeK::U;
     const int per_sm = small ? ShapeSmallK::MINB : ShapeLargeK::MINB;
     const int max_by_k = MERGE_CAP / b->max_top_k;  // the merge holds splits * k candidates
-    if (b->splits > 0) return max(1, min(min(b->splits, max_by_k), min(nvec, 64)));
-    const int max_by_work = nvec / (2 * region);  // at least two regions per CTA
-    const int cap = max(1, min(min(max_by_k, max_by_work), 64));
-    const int target = per_sm * sm_count();  // one full wave
+    if (b->splits > 0) return std::max(1, std::min(std::min(b->splits, max_by_k), std::min(nvec, 64)));
+    const int max_by_work = nvec / (2 * chunk);  // at least two chunks per CTA
+    const int cap = std::max(1, std::min(std::min(max_by_k, max_by_work), 64));
+    const int target = per_sm * smem_budget().sms;  // one full wave
     if (b->rows >= target) return 1;
-    return max(1, min(cap, (target + b->rows - 1) / b->rows));
+    return std::max(1, std::min(cap, (target + b->rows - 1) / b->rows));
 }
 
 void fill_args(KArgs& a, const MantleSampleBatch* b) {
@@ -1081,34 +1569,67 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
     a.part_cnt = nullptr;
     a.part_cap = 0;
     a.parts = 0;
-}
-
-template <typename K>
-int launch(K kernel, const KArgs& a, int grid, int threads, size_t smem, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    kernel<<<grid, threads, smem, stream>>>(a);
-    return (int)cudaGetLastError();
+    a.hist_tma_ok = a.history && reinterpret_cast<uintptr_t>(a.history) % 16 == 0 && a.hist_stride % 4 == 0;
+#ifdef MANTLE_DEBUG_SWITCHES
+    const char* dbg = getenv("MANTLE_SAMPLER_DEBUG");
+    a.debug = dbg ? atoi(dbg) : 0;
+#endif
 }
 
 template <class S, int MODE>
 int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
-    const size_t smem = S::SMEM_FIXED + bitmap_words(a.vocab) * sizeof(uint32_t);
-    const long long grid = (long long)a.rows * a.splits;
-    if (grid > 0x7fffffffLL) return kInvalid;
-    if (dtype == MANTLE_DTYPE_F32)
-        return launch(scan_rows_kernel<S, float, MODE>, a, (int)grid, S::NT, smem, stream);
-    return launch(scan_rows_kernel<S, bf16_t, MODE>, a, (int)grid, S::NT, smem, stream);
+    const SmemBudget bud = smem_budget();
+    int stages = 0, ctas = 0;
+    size_t smem = 0;
+    if (!plan_ring<S>(a.vocab, bud, &stages, &ctas, &smem)) return kInvalid;
+    const long long items = (long long)a.rows * a.splits;
+    if (items > 0x7fffffffLL) return kInvalid;
+    const int grid = (int)std::min<long long>(items, (long long)ctas * bud.sms);
+    cudaError_t e;
+    if (dtype == MANTLE_DTYPE_F32) {
+        auto kern = scan_rows_kernel<S, float, MODE>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, S::NT, smem, stream>>>(a, stages);
+    } else {
+        auto kern = scan_rows_kernel<S, bf16_t, MODE>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, S::NT, smem, stream>>>(a, stages);
+    }
+    return (int)cudaGetLastError();
 }
 
 template <int MODE>
 int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
+    if (use_alt_shape(a.max_top_k)) return launch_scan_shape<ShapeAlt, MODE>(a, dtype, stream);
     if (use_small_shape(a.max_top_k)) return launch_scan_shape<ShapeSmallK, MODE>(a, dtype, stream);
     return launch_scan_shape<ShapeLargeK, MODE>(a, dtype, stream);
 }
 
 int launch_merge(const KArgs& a, cudaStream_t stream) {
-    return launch(merge_parts_kernel, a, a.rows, ShapeLargeK::NT, ShapeLargeK::SMEM_FIXED, stream);
+    const size_t smem = ShapeLargeK::SMEM_FIXED;
+    cudaError_t e = cudaFuncSetAttribute(merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    merge_parts_kernel<<<a.rows, ShapeLargeK::NT, smem, stream>>>(a);
+    return (int)cudaGetLastError();
+}
+
+int launch_penalty(const KArgs& a, cudaStream_t stream) {
+    const size_t smem = bitmap_words(a.vocab) * sizeof(uint32_t);
+    cudaError_t e = cudaFuncSetAttribute(penalty_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    penalty_rows_kernel<<<a.rows, PENALTY_NT, smem, stream>>>(a);
+    return (int)cudaGetLastError();
+}
+
+// The reference's in-place side effect: rewrite the logits first, then sample them as they are.
+int apply_write_back(KArgs& a, cudaStream_t stream) {
+    if (!(a.flags & MANTLE_SAMPLE_WRITE_BACK_PENALTY)) return 0;
+    int rc = 0;
+    if (a.history && !(a.flags & MANTLE_SAMPLE_PENALTY_PREAPPLIED)) rc = launch_penalty(a, stream);
+    a.flags |= MANTLE_SAMPLE_PENALTY_PREAPPLIED;
+    return rc;
 }
 
 size_t parts_bytes(int rows, int parts, int cap) {
@@ -1141,6 +1662,8 @@ extern "C" int mantleCudaSampleRows(const MantleSampleBatch* batch, void* worksp
     KArgs a;
     fill_args(a, batch);
     const int s = choose_splits(batch);
+    int rc = apply_write_back(a, stream);
+    if (rc) return rc;
     if (s == 1) return launch_scan<MODE_FUSED>(a, batch->dtype, stream);
 
     const size_t need = parts_bytes(batch->rows, s, batch->max_top_k);
@@ -1153,7 +1676,7 @@ extern "C" int mantleCudaSampleRows(const MantleSampleBatch* batch, void* worksp
     a.part_val = static_cast<float*>(workspace);
     a.part_idx = reinterpret_cast<int32_t*>(a.part_val + n * a.part_cap);
     a.part_cnt = a.part_idx + n * a.part_cap;
-    int rc = launch_scan<MODE_PARTS>(a, batch->dtype, stream);
+    rc = launch_scan<MODE_PARTS>(a, batch->dtype, stream);
     if (rc) return rc;
     return launch_merge(a, stream);
 }
@@ -1163,8 +1686,7 @@ extern "C" int mantleCudaRepeatPenaltyRowsF32(const MantleSampleBatch* batch, ma
     if (batch->flags & MANTLE_SAMPLE_PENALTY_PREAPPLIED) return kInvalid;
     KArgs a;
     fill_args(a, batch);
-    a.max_top_k = 1;
-    return launch_scan<MODE_PENALTY>(a, MANTLE_DTYPE_F32, static_cast<cudaStream_t>(stream_));
+    return launch_penalty(a, static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int mantleCudaArgMaxRowsF32(const float* x, int rows, int n, int64_t row_stride, int* out_idx,
@@ -1200,6 +1722,8 @@ extern "C" int mantleCudaSampleLocalTopK(const MantleSampleBatch* batch, int voc
     a.part_val = part_val;
     a.part_idx = part_idx;
     a.part_cnt = part_cnt;
+    int rc = apply_write_back(a, static_cast<cudaStream_t>(stream_));
+    if (rc) return rc;
     return launch_scan<MODE_PARTS>(a, batch->dtype, static_cast<cudaStream_t>(stream_));
 }
 
