@@ -1207,7 +1207,11 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_kernel(const KArgs a
         __syncthreads();
 
         // ---- stream the item's chunks -------------------------------------------------------
+#ifdef MANTLE_TRIG_EXTRA
+        const int trig = min(k + MANTLE_TRIG_EXTRA, CAP / 2);
+#else
         const int trig = min(k + max(k >> 1, 16), CAP / 2);  // cut the buffer at this many entries
+#endif
         float thr = __uint_as_float(0xff800000u);            // -inf
 
         for (int cc = 0; cc < nchunks; cc++, g_done++) {
@@ -1260,19 +1264,21 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_kernel(const KArgs a
                     // U * VEC scaled values against the threshold.
                     const bool whole = cc + 1 < nchunks;  // only the last chunk can be partial
                     uint4 rv[U];
+                    float mu[U];
                     float m = __uint_as_float(0xff800000u);
 #pragma unroll
                     for (int u = 0; u < U; u++) {
+                        mu[u] = __uint_as_float(0xff800000u);
                         if (whole || v0 + u * NT < b0) {
                             rv[u] = stage[u * NT + tid];
-                            m = fmaxf(m, vec_max_scaled<T>(rv[u], c.inv_temp));
+                            mu[u] = vec_max_scaled<T>(rv[u], c.inv_temp);
                         }
+                        m = fmaxf(m, mu[u]);
                     }
                     if (m > thr) {
 #pragma unroll
                         for (int u = 0; u < U; u++)
-                            if (whole || v0 + u * NT < b0)
-                                filter_vec<S, T, false>(rv[u], v0 + u * NT, c, thr, buf, ctl);
+                            if (mu[u] > thr) filter_vec<S, T, false>(rv[u], v0 + u * NT, c, thr, buf, ctl);
                     }
                 }
             }
