@@ -63,13 +63,14 @@ struct Shape {
     // shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [Pre] [window ids[HIST_CAP]] [ring] [bitmap]
     static constexpr size_t SMEM_FIXED = 8 * (size_t)CAP + 4 * 256 + 512 + 256 + 4 * (size_t)HIST_CAP;
 };
-// Chunks are 32 KB: measured on B200, the time one bulk copy takes to land hardly depends on
-// its size (about 0.6 us for 8, 16 and 32 KB alike), so large chunks are what carries the
-// bandwidth; two stages per CTA and two CTAs per SM reached 7.3 TB/s in a bare copy loop.
-// 256 threads x 8 vectors leaves every thread 128 registers, so nothing spills.
-using ShapeSmallK = Shape<256, 8, 2048, 256, 2>;   // top_k <= 256: 16 KB candidate buffer
+// Measured on B200 (a bare copy loop over 2.5 GB): the time one bulk copy takes to land hardly
+// depends on its size (about 0.6 us for 8, 16 and 32 KB alike) and deeper rings do not raise a
+// CTA's copy rate, so bandwidth comes from chunk size times CTAs per SM.  With the sampler's
+// serial phases per row (bitmap, cuts, tail) three CTAs of 256 threads with 16 KB chunks
+// overlap better than two with 32 KB chunks (71 % against 69 % of measured HBM bandwidth).
+using ShapeSmallK = Shape<256, 4, 2048, 256, 3>;   // top_k <= 256: 16 KB candidate buffer
 using ShapeLargeK = Shape<512, 4, 4096, KMAX, 1>;  // top_k <= 1024: 32 KB candidate buffer
-using ShapeAlt = Shape<512, 4, 2048, 256, 2>;      // tuning: MANTLE_SAMPLER_SHAPE=alt
+using ShapeAlt = Shape<256, 8, 2048, 256, 2>;      // tuning: MANTLE_SAMPLER_SHAPE=alt (32 KB chunks)
 constexpr int MAX_NWARP = 32;
 constexpr int MERGE_CAP = ShapeLargeK::CAP;
 
