@@ -178,6 +178,31 @@ int mantleCudaSampleRowsHost(const MantleSampleBatch* host_batch, void* device_w
 /* Bytes of device workspace mantleCudaSampleRowsHost needs for this batch. */
 int mantleCudaSamplerHostWorkspaceBytes(const MantleSampleBatch* host_batch, size_t* bytes);
 
+/*
+ * mantleCudaSampleRows for callers that cannot supply a workspace.  It has no counterpart in
+ * the reference; it exists for hosts that must not allocate device memory where they sample
+ * -- a runtime whose device-memory plan is frozen before the decode loop starts, an embedding
+ * that keeps the allocator out of that loop -- and therefore have nowhere to take the split-row
+ * scratch from.  The scratch is a fixed array of mantleCudaSamplerStaticScratchBytes() bytes
+ * (4 MiB) inside the library image; every GPU that loads the library holds it until the
+ * process exits.  Batches that need more (rows * splits * max_top_k * 8 bytes, plus counts) are
+ * refused with cudaErrorInvalidValue and a message from mantleCudaSamplerLastError(); batches
+ * that run one CTA per row need no scratch and always fit.  The call itself allocates and
+ * frees nothing.  Its first call on a device looks the array's device address up
+ * (cudaGetSymbolAddress, with that device current) and should therefore come before any
+ * stream capture on that device.  All calls on a device share the one array, which keeps
+ * whatever the last call left in it (each call overwrites every slot it reads): calls that
+ * overlap on the GPU -- two streams, two host threads -- race on it and must be serialised
+ * by the caller.
+ */
+int mantleCudaSampleRowsNoAlloc(const MantleSampleBatch* batch, mantleCudaStream_t stream);
+
+/* Size of the static scratch behind mantleCudaSampleRowsNoAlloc. */
+size_t mantleCudaSamplerStaticScratchBytes(void);
+
+/* Text of the last refusal of mantleCudaSampleRowsNoAlloc on the calling thread ("" if none). */
+const char* mantleCudaSamplerLastError(void);
+
 /* Library version, for the loader's sanity check. */
 int mantleCudaSamplerAbiVersion(void);
 

@@ -23,10 +23,12 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "../../include/mantle_cuda_sampler.h"
 
@@ -1856,4 +1858,81 @@ extern "C" int mantleCudaSampleRowsHost(const MantleSampleBatch* hb, void* devic
         MANTLE_TRY(cudaMemcpyAsync(const_cast<void*>(hb->logits), ws + p.logits, p.logits_bytes, cudaMemcpyDeviceToHost, stream));
 #undef MANTLE_TRY
     return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// An entry point that allocates nothing.
+//
+// Some hosts cannot hand the sampler a workspace: a runtime that froze its device-memory
+// plan before sampling was wired in, an embedding whose allocator is off limits inside the
+// decode loop, a caller that may not call cudaMalloc at all at that point.  For them the
+// scratch that split rows need (the per-CTA shortlists between the streaming kernel and the
+// merge) lives in a fixed array inside the library image.  Every GPU that loads the library
+// carries the array until the process exits, which is why it is kept small.
+
+namespace {
+
+constexpr size_t kStaticScratchBytes = (size_t)4 << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_split_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices];    // device address of g_split_scratch, per device ordinal
+bool g_scratch_known[kMaxDevices];
+std::mutex g_scratch_mutex;
+thread_local char g_last_error[256];
+
+void set_last_error(const char* fmt, unsigned long long a = 0, unsigned long long b = 0) {
+    snprintf(g_last_error, sizeof g_last_error, fmt, a, b);
+}
+
+// In host code the array's name is only a handle: the address kernels can use has to be asked
+// for, per device, with that device current.
+int static_scratch(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) {
+        set_last_error("device ordinal %llu is beyond the %llu devices the static scratch tracks",
+                       (unsigned long long)dev, (unsigned long long)kMaxDevices);
+        return kInvalid;
+    }
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_known[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_split_scratch);
+        if (e != cudaSuccess) {
+            set_last_error("cudaGetSymbolAddress failed with cudaError %llu", (unsigned long long)e);
+            return (int)e;
+        }
+        g_scratch_addr[dev] = p;
+        g_scratch_known[dev] = true;
+    }
+    *out = g_scratch_addr[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" const char* mantleCudaSamplerLastError(void) { return g_last_error; }
+
+extern "C" size_t mantleCudaSamplerStaticScratchBytes(void) { return kStaticScratchBytes; }
+
+extern "C" int mantleCudaSampleRowsNoAlloc(const MantleSampleBatch* batch, mantleCudaStream_t stream_) {
+    g_last_error[0] = 0;
+    if (!batch_ok(batch, true)) {
+        set_last_error("invalid batch descriptor");
+        return kInvalid;
+    }
+    const int s = choose_splits(batch);
+    const size_t need = s > 1 ? parts_bytes(batch->rows, s, batch->max_top_k) : 0;
+    if (need > kStaticScratchBytes) {
+        set_last_error("batch needs %llu bytes of scratch, the static scratch holds %llu: pass a workspace to "
+                       "mantleCudaSampleRows instead, or lower rows * splits * max_top_k",
+                       (unsigned long long)need, (unsigned long long)kStaticScratchBytes);
+        return kInvalid;
+    }
+    void* scratch = nullptr;
+    const int rc = static_scratch(&scratch);
+    if (rc) return rc;
+    return mantleCudaSampleRows(batch, scratch, kStaticScratchBytes, stream_);
 }

@@ -80,6 +80,9 @@ EXPORTS = {
     ),
     "mantleCudaSampleRowsHost": (C.c_int, [C.POINTER(SampleBatch), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mantleCudaSamplerHostWorkspaceBytes": (C.c_int, [C.POINTER(SampleBatch), C.POINTER(C.c_size_t)]),
+    "mantleCudaSampleRowsNoAlloc": (C.c_int, [C.POINTER(SampleBatch), C.c_void_p]),
+    "mantleCudaSamplerStaticScratchBytes": (C.c_size_t, []),
+    "mantleCudaSamplerLastError": (C.c_char_p, []),
     "mantleCudaSampleMergeParts": (
         C.c_int,
         [C.POINTER(SampleBatch), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p],

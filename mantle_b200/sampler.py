@@ -332,3 +332,17 @@ class HostBatchPlan:
                                                    _stream_ptr(stream))
         native.check(rc, "mantleCudaSampleRowsHost")
         return self.out
+
+
+def launch_no_alloc(plan, stream=None):
+    """Queues `plan`'s batch through mantleCudaSampleRowsNoAlloc: the same sampling, with the
+    split-row scratch taken from the library's fixed device array instead of the plan's
+    workspace.  For callers that cannot allocate device memory where they sample.  Raises
+    CudaError carrying the library's message when the batch does not fit the fixed array."""
+    rc = plan.lib.mantleCudaSampleRowsNoAlloc(C.byref(plan.batch), _stream_ptr(stream))
+    if rc != 0:
+        msg = plan.lib.mantleCudaSamplerLastError()
+        err = native.CudaError(rc, "mantleCudaSampleRowsNoAlloc")
+        err.args = (err.args[0] + (": " + msg.decode() if msg else ""),)
+        raise err
+    return plan.out
