@@ -38,8 +38,10 @@ NOMINAL_HBM_GBS = 8000.0
 
 # DRAM bytes one launch of the streaming kernel moves per algorithmic byte, from the ncu
 # capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the
-# algorithmic bytes of the captured launch).  None until a capture has been read.
-DRAM_TRAFFIC_RATIO = None
+# algorithmic bytes of the captured launch): profiles/scan_rows_kernel_1776rows_full.md,
+# 1.0869 GB read + 0.0168 GB written for 1.0866 GB of rows.  Traffic grows with the rows
+# processed, so a full launch is this ratio times its algorithmic bytes.
+DRAM_TRAFFIC_RATIO = 1.016
 
 
 def load_oracle():
