@@ -19,10 +19,11 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libmantle_cuda_sampler.so")
 
-SOURCES = ["sampler_kernels.cu"]
+SOURCES = ["sampler_kernels.cu", "host_sampler.cu"]
 HEADERS = [
     os.path.join(ROOT, "include", "mantle_cuda_sampler.h"),
     os.path.join(ROOT, "include", "mantle_sample_params.h"),
+    os.path.join(ROOT, "include", "mantle_host_sampler.h"),
 ]
 
 NVCC_FLAGS = [

@@ -89,6 +89,40 @@ EXPORTS = {
     ),
 }
 
+
+
+class SamplerConfigC(C.Structure):
+    """MantleSamplerConfig, include/mantle_sample_params.h: logits.SamplerConfig field for field."""
+
+    _fields_ = [
+        ("seed", C.c_int64),
+        ("temperature", C.c_float),
+        ("top_k", C.c_int32),
+        ("top_p", C.c_float),
+        ("min_p", C.c_float),
+        ("repeat_penalty", C.c_float),
+        ("repeat_last_n", C.c_int32),
+    ]
+
+
+# include/mantle_host_sampler.h
+HOST_EXPORTS = {
+    "mantleSamplerNew": (C.c_void_p, [C.POINTER(SamplerConfigC), C.c_int]),
+    "mantleSamplerFree": (None, [C.c_void_p]),
+    "mantleSamplerParams": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mantleSamplerCanUseDeviceGreedy": (C.c_int, [C.c_void_p]),
+    "mantleSamplerNeedsUniform": (C.c_int, [C.c_void_p]),
+    "mantleSamplerSample": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_double, C.POINTER(C.c_int)],
+    ),
+    "mantleSamplerSampleDevice": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_double, C.c_void_p,
+         C.POINTER(C.c_int)],
+    ),
+}
+
 _lib = None
 
 
@@ -118,7 +152,7 @@ def load():
     if not os.path.exists(path):
         raise RuntimeError("CUDA sampler library missing: %s (run python -m mantle_b200.build)" % path)
     L = C.CDLL(path)
-    for name, (res, args) in EXPORTS.items():
+    for name, (res, args) in list(EXPORTS.items()) + list(HOST_EXPORTS.items()):
         f = getattr(L, name)  # AttributeError here means the build is broken: do not hide it
         f.restype = res
         f.argtypes = args

@@ -346,3 +346,80 @@ def launch_no_alloc(plan, stream=None):
         err.args = (err.args[0] + (": " + msg.decode() if msg else ""),)
         raise err
     return plan.out
+
+
+class Sampler:
+    """logits.Sampler (internal/logits/sampler.go:44-98) over the C++ host object of
+    include/mantle_host_sampler.h: NewSampler -> Sampler(cfg), Sample -> sample(), and
+    CanUseDeviceGreedy.  The uniform draw is the caller's (the reference draws rng.Float64()
+    once per non-greedy Sample; `rng` here is any callable returning a float in [0,1))."""
+
+    def __init__(self, cfg, max_vocab, rng=None, device="cuda:0"):
+        self.lib = native.load()
+        self.device = torch.device(device)
+        c = native.SamplerConfigC(cfg.seed, cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p, cfg.repeat_penalty,
+                                  cfg.repeat_last_n)
+        with torch.cuda.device(self.device):
+            self.handle = self.lib.mantleSamplerNew(C.byref(c), max_vocab)
+        if not self.handle:
+            raise RuntimeError("mantleSamplerNew failed")
+        if rng is None:
+            gen = np.random.default_rng(cfg.seed if cfg.seed >= 0 else None)
+            rng = gen.random
+        self.rng = rng
+
+    def close(self):
+        if self.handle:
+            with torch.cuda.device(self.device):
+                self.lib.mantleSamplerFree(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def params(self):
+        p = np.zeros(1, dtype=PARAMS_DTYPE)
+        native.check(self.lib.mantleSamplerParams(self.handle, p.ctypes.data_as(C.c_void_p)), "mantleSamplerParams")
+        return p[0]
+
+    def can_use_device_greedy(self):
+        return bool(self.lib.mantleSamplerCanUseDeviceGreedy(self.handle))
+
+    def _draw(self):
+        # one draw per call that takes the stochastic path, none otherwise (sampler.go:140-142, 224)
+        return float(self.rng()) if self.lib.mantleSamplerNeedsUniform(self.handle) else 0.0
+
+    @staticmethod
+    def _ids(ids):
+        a = np.ascontiguousarray([] if ids is None else ids, dtype=np.int64)
+        return a, (a.ctypes.data_as(C.c_void_p) if a.size else None)
+
+    def sample(self, logits, recent=None, exclude_penalty=None):
+        """Sample(logits, recent, excludePenalty): `logits` is a float32 numpy vector, patched in
+        place by the repeat penalty as the reference patches its slice.  Returns the token id."""
+        if logits.dtype != np.float32 or logits.ndim != 1 or not logits.flags.c_contiguous:
+            raise ValueError("logits must be a contiguous float32 vector")
+        if logits.size == 0:
+            raise ValueError("argmax: empty slice")  # the reference panics (sampler.go:239)
+        r, rp = self._ids(recent)
+        x, xp = self._ids(exclude_penalty)
+        tok = C.c_int(-1)
+        with torch.cuda.device(self.device):
+            rc = self.lib.mantleSamplerSample(self.handle, logits.ctypes.data_as(C.c_void_p), logits.size, rp, r.size,
+                                              xp, x.size, self._draw(), C.byref(tok))
+        native.check(rc, "mantleSamplerSample")
+        return tok.value
+
+    def sample_device(self, logits, recent=None, exclude_penalty=None):
+        """The same on a float32 CUDA vector that stays on the GPU (and is left untouched)."""
+        r, rp = self._ids(recent)
+        x, xp = self._ids(exclude_penalty)
+        tok = C.c_int(-1)
+        with torch.cuda.device(self.device):
+            rc = self.lib.mantleSamplerSampleDevice(self.handle, _ptr(logits), logits.numel(), rp, r.size, xp, x.size,
+                                                    self._draw(), _stream_ptr(None), C.byref(tok))
+        native.check(rc, "mantleSamplerSampleDevice")
+        return tok.value
