@@ -64,7 +64,9 @@ def test_sample_matches_oracle_and_patches_the_slice_in_place():
         recent = rng.integers(-5, V + 5, size=int(rng.integers(0, 700))).astype(np.int64)
         exclude = rng.integers(0, V, size=2).astype(np.int64)
         p = O.normalize(uniform=u, **cfg)
-        assert s.params()[["temperature", "top_k", "top_p", "repeat_last_n", "greedy"]] == p[["temperature", "top_k", "top_p", "repeat_last_n", "greedy"]]
+        got_p = s.params()
+        for field in ("temperature", "top_k", "top_p", "min_p", "repeat_penalty", "repeat_last_n", "greedy"):
+            assert got_p[field] == p[field], field
         want_logits = logits.copy()[None, :]
         ref = O.sample_rows(want_logits, np.array([p]), history=recent.astype(np.int32)[None, :] if recent.size else None,
                             exclude=exclude.astype(np.int32))
