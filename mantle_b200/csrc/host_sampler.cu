@@ -67,8 +67,7 @@ int stage(MantleHostSampler* s, MantleSampleBatch* b, int n, const int64_t* rece
     b->rows = 1;
     b->vocab = n;
     b->row_stride = n;
-    b->max_top_k = s->params.top_k < MANTLE_SAMPLE_MAX_TOP_K ? s->params.top_k : MANTLE_SAMPLE_MAX_TOP_K;
-    if (b->max_top_k > n) b->max_top_k = n;
+    b->max_top_k = s->params.top_k < n ? s->params.top_k : n;  // sampler.go:147
     b->history = window > 0 ? s->h_hist : nullptr;
     b->hist_stride = window;
     b->exclude = n_exclude > 0 ? s->h_excl : nullptr;

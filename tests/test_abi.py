@@ -55,7 +55,7 @@ def test_invalid_arguments_are_rejected_on_the_host():
     assert lib.mantleCudaSamplerWorkspaceBytes(C.byref(good_batch()), C.byref(n)) == 0
     mutations = [
         ("logits", 0), ("rows", 0), ("vocab", 0), ("vocab", native.MAX_VOCAB + 1), ("dtype", 7),
-        ("row_stride", 999), ("max_top_k", 0), ("max_top_k", native.MAX_TOP_K + 1), ("params", 0), ("next", 0),
+        ("row_stride", 999), ("max_top_k", 0), ("max_top_k", native.MAX_VOCAB + 1), ("params", 0), ("next", 0),
         ("n_exclude", 3), ("hist_stride", -1), ("flags", 8), ("reserved", 1), ("splits", -1), ("logits", 0x1001),
     ]
     for field, value in mutations:
@@ -66,6 +66,9 @@ def test_invalid_arguments_are_rejected_on_the_host():
     b = good_batch()
     b.cand_idx = 0x4000  # candidates wanted but no room per row
     assert lib.mantleCudaSampleRows(C.byref(b), None, 0, None) == inv
+    b = good_batch()
+    b.max_top_k, b.cand_idx, b.cand_prob, b.cand_stride = native.MAX_TOP_K + 1, 0x4000, 0x5000, 8
+    assert lib.mantleCudaSampleRows(C.byref(b), None, 0, None) == inv  # long shortlists are never materialised
     b = good_batch()
     b.dtype = native.DTYPE_BF16
     b.flags = native.FLAG_WRITE_BACK_PENALTY  # bf16 rows cannot hold the penalised value

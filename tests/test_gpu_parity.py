@@ -338,3 +338,64 @@ def test_host_buffer_entry_point():
             assert int(out.status.item()) == 0
             want = ref_logits if flags else logits
             assert np.array_equal(plan.logits.numpy(), want)
+
+
+# ---- long shortlists: top_k above 1024, up to the whole vocabulary ---------------------------------------
+
+def wide_check(logits_np, params, history=None, exclude=None, bf16=False, where=""):
+    """Long shortlists are never materialised: token, shortlist length and nucleus length are what
+    both sides report.  The oracle orders the whole row (the stand-in for the reference's O(V*k)
+    insertion loop, proven equal to it on small cases)."""
+    if bf16:
+        dev = torch.from_numpy(logits_np.view(np.int16).copy()).to(DEV).view(torch.bfloat16)
+    else:
+        dev = torch.from_numpy(logits_np.copy()).to(DEV)
+    max_k = int(max(params["top_k"].max(), 1025))
+    gpu = run_gpu(dev, params, max_k, history, None, exclude, 0)
+    ref = O.sample_rows(logits_np.copy(), params, history=history, exclude=exclude, cand_cap=0)
+    compare(gpu, ref, 0, where=where)
+    assert gpu["status"] == 0
+    return gpu, ref
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_long_shortlists_small_vocab(seed):
+    rng = np.random.default_rng(900 + seed)
+    rows, V = 40, int(rng.choice([1500, 4097, 9000]))
+    logits = (rng.standard_normal((rows, V)) * 2).astype(np.float32)
+    if seed % 2:
+        logits = (np.round(logits * 8) / 8).astype(np.float32)  # tie groups of dozens of columns
+    params = np.zeros(rows, dtype=O.PARAMS_DTYPE)
+    for r in range(rows):
+        params[r] = O.normalize(
+            temperature=float(rng.choice([0.0, 0.7, 1.0, 1.3])),
+            top_k=int(rng.choice([1100, V // 2 + 600, V, 2 * V])),
+            top_p=float(rng.choice([0.3, 0.9, 0.97, 1.0])),
+            min_p=float(rng.choice([0.0, 0.0, 0.02, 0.3])),
+            repeat_penalty=float(rng.choice([1.0, 1.2])),
+            repeat_last_n=64,
+            uniform=float(rng.choice([0.0, rng.random(), rng.random(), 1.0 - 2.0 ** -53])),
+        )
+    hist = rng.integers(0, V, size=(rows, 64)).astype(np.int32)
+    exclude = rng.integers(0, V, size=2).astype(np.int32)
+    wide_check(logits, params, history=hist, exclude=exclude, where="seed %d V %d" % (seed, V))
+
+
+def test_long_shortlist_degenerate_rows():
+    V = 3000
+    logits = np.zeros((4, V), dtype=np.float32)           # one tie group holds everything
+    logits[1] = np.where(np.arange(V) % 2 == 0, 1.0, -1.0)  # two tie groups
+    logits[2, 7] = 50.0                                    # one column takes all the mass
+    logits[3] = np.linspace(-3, 3, V, dtype=np.float32)
+    params = np.array([O.normalize(temperature=1.0, top_k=V, top_p=0.9, uniform=u) for u in (0.5, 0.7, 0.99, 0.123)])
+    wide_check(logits, params)
+    params = np.array([O.normalize(temperature=1.0, top_k=1500, top_p=1.0, uniform=u) for u in (0.999999, 0.7, 0.99, 0.123)])
+    wide_check(logits, params)
+
+
+def test_config_full_vocab_nucleus():
+    """BASELINE config 2: 256 bf16 rows, vocab 128 256, top_k = V, top_p 0.9, temperature 1."""
+    w = workloads.make("full_vocab_nucleus", device=DEV)
+    bits = to_bf16_bits(w.logits)
+    gpu, ref = wide_check(bits, w.params, bf16=True)
+    assert np.all(ref["n_kept"] == w.vocab) and ref["cut"].min() > 1000  # tens of thousands of nucleus entries
