@@ -36,6 +36,14 @@ UNIT = "rows/s"
 FALLBACK_HBM_GBS = 6650.0
 NOMINAL_HBM_GBS = 8000.0
 
+WORKLOAD_NOTES = {
+    "single_row": "temp 0.6 top_k 20 top_p 0.95 repeat_penalty 1.1, seeded N(0,3^2) logits with 16 boosted ids",
+    "throughput": "temp 0.6 top_k 20 top_p 0.95 repeat_penalty 1.1, seeded N(0,3^2) logits with 16 boosted ids per row",
+    "mixed_batch": "per-row temp U[0.2,1.5] top_k {40,1,20,50,200} top_p U[0.8,1] repeat_penalty U[1,1.3], "
+                   "seeded N(0,3^2) logits with Zipf(1.1) spikes",
+    "full_vocab_nucleus": "temp 1.0 top_k = vocabulary top_p 0.9 no penalty, seeded N(0,2^2) logits rounded to bf16",
+}
+
 # DRAM bytes one launch of the streaming kernel moves per algorithmic byte, from the ncu
 # capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the
 # algorithmic bytes of the captured launch): profiles/scan_rows_kernel_1776rows_full.md,
@@ -184,7 +192,10 @@ def cpu_baseline(O, w, seconds=3.0):
     """Times the CPU port of the reference sampler with every host thread (one sampler state
     per row, rows handed out dynamically) on a bounded sample: whole passes over the
     workload's first rows, repeated until `seconds` of wall time have gone by."""
-    logits = w.logits.cpu().numpy()
+    if w.logits.dtype == torch.bfloat16:  # the CPU port takes bfloat16 rows as uint16 bit patterns
+        logits = w.logits.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    else:
+        logits = w.logits.cpu().numpy()
     hist = None if w.history is None else w.history.cpu().numpy()
     n = min(w.rows, 4096)
     first = O.sample_rows(logits[:n].copy(), w.params[:n], history=None if hist is None else hist[:n])  # warm-up
@@ -326,18 +337,20 @@ def run_ours(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
-                "workload": "%s: %d rows x %d f32 columns per GPU, history %d ids, temp 0.6 top_k 20 top_p 0.95 "
-                            "repeat_penalty 1.1, seeded N(0,3^2) logits with 16 boosted ids per row"
-                            % (args.workload, w.rows, w.vocab, 0 if w.history is None else w.history.shape[1]),
+                "workload": "%s: %d rows x %d %s columns per GPU, history %d ids, %s"
+                            % (args.workload, w.rows, w.vocab, "bf16" if w.logits.dtype == torch.bfloat16 else "f32",
+                               0 if w.history is None else w.history.shape[1], WORKLOAD_NOTES.get(args.workload, "")),
                 "rows_per_gpu": w.rows, "vocab": w.vocab, "parallelism": "rows sharded over %d GPU(s), no collective" % world,
-                "l2": "inputs (%.2f GB per GPU) exceed the 126 MB L2, no flush needed" % (kernel_bytes / 1e9),
+                "l2": ("inputs (%.2f GB per GPU) exceed the 126 MB L2, no flush needed" % (kernel_bytes / 1e9))
+                      if kernel_bytes > 2 * 126e6 else
+                      ("inputs (%.1f MB) fit the 126 MB L2 and are not flushed: an L2-resident timing" % (kernel_bytes / 1e6)),
                 "ctas_per_row": plan.splits,
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None if DRAM_TRAFFIC_RATIO is None else DRAM_TRAFFIC_RATIO * kernel_bytes,
+                "traffic": DRAM_TRAFFIC_RATIO * kernel_bytes if args.workload == "throughput" else None,
                 "peak_kind": "of %s" % peak_kind, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                "kernel": "scan_rows_kernel<float, fused>", "algorithmic_bytes_per_launch": kernel_bytes,
+                "kernel": "wide_rows_kernel" if w.max_top_k > 1024 else "scan_rows_kernel", "algorithmic_bytes_per_launch": kernel_bytes,
                 "bytes_per_row": w.bytes_per_row,
             },
             "cpu_baseline": cpu,
