@@ -38,8 +38,10 @@ typedef void* mantleCudaStream_t; /* a cudaStream_t, as in native/softmax.h:11 *
 #define MANTLE_DTYPE_F32 0
 #define MANTLE_DTYPE_BF16 1
 
-/* Largest top_k the shortlist kernels take.  The reference's shortlist loop is
- * O(V*k) and meant for small k (sampler.go:252-254); its default is 40. */
+/* Largest top_k the streaming shortlist kernels take.  The reference's shortlist loop is
+ * O(V*k) and meant for small k (sampler.go:252-254); its default is 40.  Batches with a
+ * larger max_top_k (up to the vocabulary: the reference's whole-vocabulary nucleus,
+ * TopK >= V) run on a slower kernel that never materialises the shortlist. */
 #define MANTLE_SAMPLE_MAX_TOP_K 1024
 /* Largest vocabulary (per GPU) the kernels take: the penalty bitmap of V bits lives
  * in shared memory beside the candidate buffer. */
@@ -79,8 +81,9 @@ typedef void* mantleCudaStream_t; /* a cudaStream_t, as in native/softmax.h:11 *
  *   n_kept, cut optional out, [rows]: shortlist length after min-p and nucleus length
  *               after top-p; both 0 on greedy rows
  *   status      optional out: one int32 the kernels OR status bits into
- *   max_top_k   an upper bound of params[r].top_k over the batch,
- *               1..MANTLE_SAMPLE_MAX_TOP_K; sizes the workspace
+ *   max_top_k   an upper bound of min(params[r].top_k, vocab) over the batch; sizes the
+ *               workspace.  Above MANTLE_SAMPLE_MAX_TOP_K the whole batch takes the
+ *               long-shortlist kernel: cand_idx/cand_prob must then be NULL
  *   splits      CTAs per row: 0 lets the library choose (1 for batches that fill the
  *               GPU, more for small batches); > 1 needs the workspace
  */
