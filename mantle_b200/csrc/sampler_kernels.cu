@@ -2200,6 +2200,16 @@ int forced_shape() {
     return forced;
 }
 
+// MANTLE_SAMPLER_KERNEL=ldg|tma picks the streaming kernel for shortlists of at most 256 entries.
+int forced_kernel() {
+    static const int forced = [] {
+        const char* e = getenv("MANTLE_SAMPLER_KERNEL");
+        if (!e) return 0;
+        return strcmp(e, "ldg") == 0 ? 1 : (strcmp(e, "tma") == 0 ? 2 : 0);
+    }();
+    return forced;
+}
+
 bool use_small_shape(int max_top_k) {
     if (max_top_k > ShapeSmallK::KCAP) return false;
     return forced_shape() != 2;
@@ -2319,16 +2329,6 @@ int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
         kern<<<grid, S::NT, smem, stream>>>(a, stages);
     }
     return (int)cudaGetLastError();
-}
-
-// MANTLE_SAMPLER_KERNEL=ldg|tma picks the streaming kernel for shortlists of at most 256 entries.
-int forced_kernel() {
-    static const int forced = [] {
-        const char* e = getenv("MANTLE_SAMPLER_KERNEL");
-        if (!e) return 0;
-        return strcmp(e, "ldg") == 0 ? 1 : (strcmp(e, "tma") == 0 ? 2 : 0);
-    }();
-    return forced;
 }
 
 template <int MODE>
