@@ -72,6 +72,9 @@ struct Shape {
 // overlap better than two with 32 KB chunks (71 % against 69 % of measured HBM bandwidth).
 using ShapeSmallK = Shape<256, 4, 2048, 256, 3>;   // top_k <= 256: 16 KB candidate buffer
 using ShapeLargeK = Shape<512, 4, 4096, KMAX, 1>;  // top_k <= 1024: 32 KB candidate buffer
+#ifndef LDG_PREFETCH
+#define LDG_PREFETCH 1
+#endif
 #ifndef LDG_NT
 #define LDG_NT 256
 #define LDG_U 4
@@ -1484,7 +1487,24 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             dst[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
         }
     };
-    if (!careful && nreg > 0) load(ra, 0);
+    // `ahead(r)`: ask the L2 for region r (one request per 128-byte line), two regions before its
+    // loads are issued, so that those loads find their lines on the way or already there
+    auto ahead = [&](int r) {
+#if LDG_PREFETCH
+        if (r < nreg && (tid & 7) == 0) {
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                int v = a0 + r * RV + u * NT + tid;
+                if (v < b0) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(vbase + v));
+            }
+        }
+#endif
+    };
+    if (!careful && nreg > 0) {
+        load(ra, 0);
+        ahead(1);
+        ahead(2);
+    }
     if (tid == 0) ctl->cnt = 0;
 
     // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
@@ -1572,10 +1592,12 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         int r = 1;
         while (r < nreg && !careful) {
             if (r + 1 < nreg) load(ra, r + 1);
+            ahead(r + 3);
             later(rb, r);
             region_end(trig);
             if (++r >= nreg || careful) break;
             if (r + 1 < nreg) load(rb, r + 1);
+            ahead(r + 3);
             later(ra, r);
             region_end(trig);
             ++r;
