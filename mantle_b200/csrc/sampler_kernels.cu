@@ -72,6 +72,9 @@ struct Shape {
 // overlap better than two with 32 KB chunks (71 % against 69 % of measured HBM bandwidth).
 using ShapeSmallK = Shape<256, 4, 2048, 256, 3>;   // top_k <= 256: 16 KB candidate buffer
 using ShapeLargeK = Shape<512, 4, 4096, KMAX, 1>;  // top_k <= 1024: 32 KB candidate buffer
+#ifndef LDG_VOTE_EVERY
+#define LDG_VOTE_EVERY 2
+#endif
 #ifndef LDG_PREFETCH
 #define LDG_PREFETCH 1
 #endif
@@ -1589,17 +1592,20 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         region_end(k + 1);
 
         // -- regions 1.. : two register sets, each refilled while the other is filtered --
+        // The barrier carries only the vote (the register sets are private), so it need not follow
+        // every region: the threshold is refreshed at most every LDG_VOTE_EVERY regions, at the
+        // price of a few more survivors under a threshold that is that much staler.
         int r = 1;
         while (r < nreg && !careful) {
             if (r + 1 < nreg) load(ra, r + 1);
             ahead(r + 3);
             later(rb, r);
-            region_end(trig);
+            if (r % LDG_VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
             if (++r >= nreg || careful) break;
             if (r + 1 < nreg) load(rb, r + 1);
             ahead(r + 3);
             later(ra, r);
-            region_end(trig);
+            if (r % LDG_VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
             ++r;
         }
     }
