@@ -46,10 +46,10 @@ WORKLOAD_NOTES = {
 
 # DRAM bytes one launch of the streaming kernel moves per algorithmic byte, from the ncu
 # capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the
-# algorithmic bytes of the captured launch): profiles/scan_rows_kernel_1776rows_full.md,
-# 1.0869 GB read + 0.0168 GB written for 1.0866 GB of rows.  Traffic grows with the rows
+# algorithmic bytes of the captured launch): profiles/scan_rows_ldg_kernel_2368rows_full.md,
+# 1.4509 GB read + 0.0061 GB written for 1.4488 GB of rows.  Traffic grows with the rows
 # processed, so a full launch is this ratio times its algorithmic bytes.
-DRAM_TRAFFIC_RATIO = 1.016
+DRAM_TRAFFIC_RATIO = 1.006
 
 
 def load_oracle():
@@ -350,7 +350,7 @@ def run_ours(args):
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": DRAM_TRAFFIC_RATIO * kernel_bytes if args.workload == "throughput" else None,
                 "peak_kind": "of %s" % peak_kind, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                "kernel": "wide_rows_kernel" if w.max_top_k > 1024 else "scan_rows_kernel", "algorithmic_bytes_per_launch": kernel_bytes,
+                "kernel": "wide_rows_kernel" if w.max_top_k > 1024 else ("scan_rows_ldg_kernel" if w.max_top_k <= 256 else "scan_rows_kernel"), "algorithmic_bytes_per_launch": kernel_bytes,
                 "bytes_per_row": w.bytes_per_row,
             },
             "cpu_baseline": cpu,
