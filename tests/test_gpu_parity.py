@@ -399,3 +399,20 @@ def test_config_full_vocab_nucleus():
     bits = to_bf16_bits(w.logits)
     gpu, ref = wide_check(bits, w.params, bf16=True)
     assert np.all(ref["n_kept"] == w.vocab) and ref["cut"].min() > 1000  # tens of thousands of nucleus entries
+
+
+@pytest.mark.parametrize("H", [1501, 3000, 1024])
+def test_history_layouts(H):
+    """History rows that cannot be staged by a bulk copy (odd stride), that exceed the staged
+    window, and that fit it exactly; shortlists of 20 (plain-load kernel) and 400 (ring kernel)."""
+    rng = np.random.default_rng(H)
+    rows, V = 12, 70001
+    logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    hist = rng.integers(-1, V + 1, size=(rows, H)).astype(np.int32)
+    hist_len = rng.integers(H // 2, H + 1, size=rows).astype(np.int32)
+    exclude = hist[0, :3].copy()
+    for k, last_n in [(20, 64), (20, 5000), (400, 5000), (400, 700)]:
+        params = np.array([O.normalize(temperature=0.8, top_k=k, top_p=0.95, repeat_penalty=1.3, repeat_last_n=last_n,
+                                       uniform=float(rng.random())) for _ in range(rows)])
+        check_against_oracle(logits, params, k, history=hist, hist_len=hist_len, exclude=exclude, cand_cap=k,
+                             where="H %d k %d window %d" % (H, k, last_n))
