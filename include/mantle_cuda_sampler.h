@@ -206,6 +206,15 @@ size_t mantleCudaSamplerStaticScratchBytes(void);
 /* Text of the last refusal of mantleCudaSampleRowsNoAlloc on the calling thread ("" if none). */
 const char* mantleCudaSamplerLastError(void);
 
+/*
+ * Failure-path self-test (no counterpart in the reference): launches a kernel that waits, with
+ * the same bounded wait the bulk-copy ring uses, on a barrier nothing completes.  After
+ * limit_ns (at most one second) the kernel sets MANTLE_SAMPLE_STATUS_TIMEOUT in *status_dev and
+ * returns; the context stays usable.  Nothing faults, traps or spins without bound.
+ */
+int mantleCudaSamplerSelfTestBoundedWait(unsigned long long limit_ns, int32_t* status_dev,
+                                         mantleCudaStream_t stream);
+
 /* Library version, for the loader's sanity check. */
 int mantleCudaSamplerAbiVersion(void);
 

@@ -897,15 +897,28 @@ __device__ __forceinline__ uint64_t global_ns() {
 // Every wait on a copy is bounded by wall time: after WAIT_LIMIT_NS without the phase
 // completing the caller gives up, raises MANTLE_SAMPLE_STATUS_TIMEOUT and leaves the kernel
 // in an orderly way.  A copy normally lands within a microsecond or two.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_ns();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; i++)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+        if (global_ns() - t0 > limit_ns) return false;
     }
+}
+
+// Self-test of the bounded wait: waits on an mbarrier that nothing ever completes.  The wait
+// must give up after limit_ns, report it in the status word and leave the context usable.
+__global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, int32_t* status) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool landed = mbar_wait(&bar, 0, limit_ns);
+    if (!landed && threadIdx.x == 0) atomicOr(status, MANTLE_SAMPLE_STATUS_TIMEOUT);
 }
 
 __device__ __forceinline__ uint64_t evict_first_policy() {
@@ -2724,4 +2737,13 @@ extern "C" int mantleCudaSampleRowsNoAlloc(const MantleSampleBatch* batch, mantl
     const int rc = static_scratch(&scratch);
     if (rc) return rc;
     return mantleCudaSampleRows(batch, scratch, kStaticScratchBytes, stream_);
+}
+
+// Runs the bounded wait of the bulk-copy ring on a barrier that is never completed: after
+// limit_ns the kernel must return with MANTLE_SAMPLE_STATUS_TIMEOUT in *status_dev.
+extern "C" int mantleCudaSamplerSelfTestBoundedWait(unsigned long long limit_ns, int32_t* status_dev,
+                                                    mantleCudaStream_t stream_) {
+    if (!status_dev || limit_ns == 0 || limit_ns > 1000000000ull) return kInvalid;
+    bounded_wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream_)>>>(limit_ns, status_dev);
+    return (int)cudaGetLastError();
 }

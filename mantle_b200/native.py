@@ -18,6 +18,7 @@ FLAG_WRITE_BACK_PENALTY = 1
 FLAG_PENALTY_PREAPPLIED = 2
 STATUS_TOPK_RANGE = 1
 STATUS_EMPTY = 2
+STATUS_TIMEOUT = 4
 CUDA_ERROR_INVALID_VALUE = 1
 
 # MantleSampleParams, include/mantle_sample_params.h
@@ -83,6 +84,7 @@ EXPORTS = {
     "mantleCudaSampleRowsNoAlloc": (C.c_int, [C.POINTER(SampleBatch), C.c_void_p]),
     "mantleCudaSamplerStaticScratchBytes": (C.c_size_t, []),
     "mantleCudaSamplerLastError": (C.c_char_p, []),
+    "mantleCudaSamplerSelfTestBoundedWait": (C.c_int, [C.c_ulonglong, C.c_void_p, C.c_void_p]),
     "mantleCudaSampleMergeParts": (
         C.c_int,
         [C.POINTER(SampleBatch), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p],

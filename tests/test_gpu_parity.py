@@ -416,3 +416,24 @@ def test_history_layouts(H):
                                        uniform=float(rng.random())) for _ in range(rows)])
         check_against_oracle(logits, params, k, history=hist, hist_len=hist_len, exclude=exclude, cand_cap=k,
                              where="H %d k %d window %d" % (H, k, last_n))
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """Failure detection without a fault: a wait on a barrier nothing completes runs out after
+    its limit, the kernel reports it in the status word, and the context keeps working."""
+    import time
+
+    lib = native.load()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    t0 = time.perf_counter()
+    rc = lib.mantleCudaSamplerSelfTestBoundedWait(20_000_000, C.c_void_p(status.data_ptr()),  # 20 ms
+                                                  C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert int(status.item()) == native.STATUS_TIMEOUT
+    assert 0.015 < dt < 1.0, dt
+    assert lib.mantleCudaSamplerSelfTestBoundedWait(0, C.c_void_p(status.data_ptr()), None) == native.CUDA_ERROR_INVALID_VALUE
+    # the context is still good: sample something
+    g, _ = one([-1, 5, 3, 7, 2], temperature=0.0)
+    assert g["next"][0] == 3
