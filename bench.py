@@ -275,7 +275,11 @@ def run_ours(args):
         return run_vocab_sharded(args, world, rank, device)
     w = workloads.make(args.workload, rows=args.rows, device=device, seed=workloads.BASE_SEED + 3000 + rank)
     p_dev = sampler.params_to_device(w.params, device)
-    plan = sampler.BatchPlan(w.logits, p_dev, w.max_top_k, history=w.history, want_counts=False, splits=args.splits)
+    post = bool(args.logit_scale or args.logit_softcap)
+    if post:  # a side measurement of the fused head post-processing: the device arm only
+        args.no_e2e = args.no_cpu = True
+    plan = sampler.BatchPlan(w.logits, p_dev, w.max_top_k, history=w.history, want_counts=False, splits=args.splits,
+                             logit_scale=args.logit_scale, logit_softcap=args.logit_softcap)
     step = plan.launch
 
     clocks = ClockSampler(local)
@@ -345,12 +349,13 @@ def run_ours(args):
                       if kernel_bytes > 2 * 126e6 else
                       ("inputs (%.1f MB) fit the 126 MB L2 and are not flushed: an L2-resident timing" % (kernel_bytes / 1e6)),
                 "ctas_per_row": plan.splits,
+                **({"logit_scale": args.logit_scale, "logit_softcap": args.logit_softcap} if post else {}),
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": DRAM_TRAFFIC_RATIO * kernel_bytes if args.workload == "throughput" else None,
                 "peak_kind": "of %s" % peak_kind, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                "kernel": "wide_rows_kernel" if w.max_top_k > 1024 else ("scan_rows_ldg_kernel" if w.max_top_k <= 256 else "scan_rows_kernel"), "algorithmic_bytes_per_launch": kernel_bytes,
+                "kernel": "wide_rows_kernel" if w.max_top_k > 1024 else ("scan_rows_ldg_kernel" if (w.max_top_k <= 256 or post) else "scan_rows_kernel"), "algorithmic_bytes_per_launch": kernel_bytes,
                 "bytes_per_row": w.bytes_per_row,
             },
             "cpu_baseline": cpu,
@@ -424,6 +429,8 @@ def main():
     ap.add_argument("--workload", default="throughput")
     ap.add_argument("--rows", type=int, default=4096, help="rows per GPU")
     ap.add_argument("--splits", type=int, default=0, help="CTAs per row (0: library's choice)")
+    ap.add_argument("--logit-scale", type=float, default=0.0, help="fuse the model head's multiplier (side measurement)")
+    ap.add_argument("--logit-softcap", type=float, default=0.0, help="fuse the model head's soft cap (side measurement)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -55,6 +55,11 @@ typedef void* mantleCudaStream_t; /* a cudaStream_t, as in native/softmax.h:11 *
 /* The history is ignored: mantleCudaRepeatPenaltyRowsF32 already ran on these logits. */
 #define MANTLE_SAMPLE_PENALTY_PREAPPLIED 2u
 
+/* The soft cap uses tanhf, as the reference's device kernel does (native/softmax.cu:963-970),
+ * instead of the host path's fastTanh (simd/ops.go:165-175), which is the default because a
+ * CPU can reproduce it bit for bit. */
+#define MANTLE_SAMPLE_SOFTCAP_TANHF 4u
+
 /* bits of the optional device status word (OR-ed in by the kernels; never cleared) */
 #define MANTLE_SAMPLE_STATUS_TOPK_RANGE 1  /* a row's top_k exceeded max_top_k          */
 #define MANTLE_SAMPLE_STATUS_EMPTY 2       /* a row ended with an empty shortlist (the  */
@@ -86,6 +91,13 @@ typedef void* mantleCudaStream_t; /* a cudaStream_t, as in native/softmax.h:11 *
  *               long-shortlist kernel: cand_idx/cand_prob must then be NULL
  *   splits      CTAs per row: 0 lets the library choose (1 for batches that fill the
  *               GPU, more for small batches); > 1 needs the workspace
+ *   logit_scale, logit_softcap   the model head's post-processing, applied on the fly to every
+ *               logit before the sampler sees it and gated as the reference gates it
+ *               (simd/runtime.go:258-272): l *= logit_scale when it is neither 0 nor 1
+ *               (LMHeadMultiplier), then l = tanh(l / logit_softcap) * logit_softcap when
+ *               logit_softcap > 0 (FinalLogitSoftcap).  The logits themselves stay as they
+ *               are, so neither penalty flag may be set with it.  A negative multiplier is
+ *               refused.  Zero in both fields: no post-processing
  */
 typedef struct MantleSampleBatch {
     const void* logits;
@@ -110,6 +122,8 @@ typedef struct MantleSampleBatch {
     int32_t splits;
     uint32_t flags;
     uint32_t reserved;
+    float logit_scale;
+    float logit_softcap;
 } MantleSampleBatch;
 
 /*
@@ -132,6 +146,18 @@ int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* splits);
  * (float32), history, hist_len, exclude and params and writes only logits.
  */
 int mantleCudaRepeatPenaltyRowsF32(const MantleSampleBatch* batch, mantleCudaStream_t stream);
+
+/*
+ * The model head's post-processing alone, in place over [rows][row_stride] float32 logits:
+ * the multiplier loop and the soft cap of simd/runtime.go:258-272.  Replaces
+ * mantleCudaLogitSoftcapF32 (native/softmax.cu:963-970, native/softmax.go:62-77), which
+ * covers the cap only; `flags` takes MANTLE_SAMPLE_SOFTCAP_TANHF for that kernel's tanhf.
+ * For callers that want the rewritten logits: mantleCudaSampleRows applies the same
+ * arithmetic on the fly from the descriptor's logit_scale / logit_softcap and writes nothing.
+ */
+int mantleCudaLogitPostprocessRowsF32(float* logits, int rows, int vocab, int64_t row_stride,
+                                      float logit_scale, float logit_softcap, uint32_t flags,
+                                      mantleCudaStream_t stream);
 
 /*
  * Index of the maximum of each row, the lowest index on ties (argmax,

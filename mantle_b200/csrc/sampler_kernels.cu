@@ -84,9 +84,12 @@ using ShapeLargeK = Shape<512, 4, 4096, KMAX, 1>;  // top_k <= 1024: 32 KB candi
 #define LDG_MINB 4
 #endif
 using ShapeLdg = Shape<LDG_NT, LDG_U, 2048, 256, LDG_MINB>;  // the plain-load kernel: four CTAs per SM
+using ShapeLdgLargeK = Shape<512, 4, 4096, KMAX, 1>;         // the plain-load kernel for top_k <= 1024
 using ShapeAlt = Shape<256, 8, 2048, 256, 2>;      // tuning: MANTLE_SAMPLER_SHAPE=alt (32 KB chunks)
 constexpr int MAX_NWARP = 32;
 constexpr int MERGE_CAP = ShapeLargeK::CAP;
+
+constexpr int POST_SCALE = 1, POST_CAP = 2, POST_TANHF = 4;
 
 constexpr int MODE_FUSED = 0;    // one CTA per row, tail in the same kernel
 constexpr int MODE_PARTS = 1;    // several CTAs per row (or one vocabulary shard): write the local shortlist
@@ -163,6 +166,11 @@ struct KArgs {
     int part_cap;
     int parts;
     int hist_tma_ok;  // history base 16-byte aligned and hist_stride a multiple of 4
+    // post-processing of the model head's output, applied to every logit before the sampler
+    // sees it: POST_SCALE l *= post_scale; POST_CAP l = tanh(l / post_cap) * post_cap
+    int post_mode;
+    float post_scale;
+    float post_cap;
 #ifdef MANTLE_DEBUG_SWITCHES
     int debug;
 #endif
@@ -214,6 +222,64 @@ __device__ __forceinline__ float penalise(float l, float p) {
     return l > 0.0f ? __fdiv_rn(l, p) : __fmul_rn(l, p);
 }
 
+// fastTanh, simd/ops.go:165-175, operation for operation in float32.
+__device__ __forceinline__ float fast_tanh(float x) {
+    if (x > 10.0f) return 1.0f;
+    if (x < -10.0f) return -1.0f;
+    const float e2x = fast_exp(__fmul_rn(2.0f, x));
+    return __fdiv_rn(__fsub_rn(e2x, 1.0f), __fadd_rn(e2x, 1.0f));
+}
+
+// What the model head does to a logit before the sampler sees it (simd/runtime.go:258-272):
+// the multiplier first, then the soft cap, with the host path's fastTanh or, on request, with
+// tanhf as the reference's device kernel has it (native/softmax.cu:963-970).
+struct Post {
+    int mode;
+    float scale, cap;
+};
+__device__ __forceinline__ float post_logit(float l, const Post& p) {
+    if (p.mode & POST_SCALE) l = __fmul_rn(l, p.scale);
+    if (p.mode & POST_CAP) {
+        const float b = __fdiv_rn(l, p.cap);
+        const float t = (p.mode & POST_TANHF) ? tanhf(b) : fast_tanh(b);
+        l = __fmul_rn(t, p.cap);
+    }
+    return l;
+}
+
+// The streaming kernels never evaluate post_logit on a column that cannot matter.  The true map
+// g(l) = inv_temp * cap * tanh(l * scale / cap) is increasing, and what the device computes
+// differs from it by less than POST_EPS * cap * inv_temp (fastTanh: 1.7e-6 absolute, the
+// worst over every float32 in [-10, 10]; tanhf: 3e-7; the roundings of the multiplies and
+// divides: 3e-7 relative), so a threshold on the computed values turns into a threshold on the raw
+// logits: every column whose computed value reaches `thr` has a raw logit of at least
+// post_raw_bound(thr).  The margins are several times the error they cover; a wider margin only
+// lets a few more columns through to the exact test.
+constexpr float POST_EPS = 1e-5f;
+__device__ __forceinline__ float post_raw_bound(float thr, float inv_temp, const Post& p) {
+    const float ninf = __uint_as_float(0xff800000u);
+    if (!(thr > ninf)) return ninf;
+    float q = thr / inv_temp;
+    if (!(fabsf(q) > 1e-30f) || !(fabsf(q) < 1e30f)) return ninf;  // at zero the roundings are not relative
+    if (p.mode & POST_CAP) {
+        float y = q / p.cap - 10.0f * POST_EPS;
+        if (y <= -1.0f) return ninf;
+        y = fminf(y, 1.0f - 1e-6f);
+        q = 0.5f * logf((1.0f + y) / (1.0f - y)) * p.cap;  // atanh
+        if (!(fabsf(q) > 1e-30f)) return ninf;
+    }
+    if (p.mode & POST_SCALE) q = q / p.scale;
+    return q - fabsf(q) * 1e-4f;
+}
+// A value that at least as many columns reach as have a raw logit >= raw0 (the seed of the threshold).
+__device__ __forceinline__ float post_seed_value(float raw0, float inv_temp, const Post& p) {
+    const float ninf = __uint_as_float(0xff800000u);
+    if (!(raw0 > ninf)) return ninf;
+    const float v0 = __fmul_rn(post_logit(raw0, p), inv_temp);
+    const float slack = (p.mode & POST_CAP) ? 4.0f * POST_EPS * p.cap * inv_temp : 0.0f;
+    return v0 - slack - fabsf(v0) * 1e-5f;
+}
+
 template <typename T>
 struct Elem;
 template <>
@@ -261,6 +327,7 @@ struct RowCtx {
     float pen;
     bool pen_bitmap;      // the penalty is applied from the bitmap (logits stay read-only)
     const uint32_t* bm;   // bitmap, bit e set: column e is penalised
+    Post post;            // only read by the kernels built with POST
 };
 
 __device__ __forceinline__ bool bm_test(const uint32_t* bm, int e) { return (bm[e >> 5] >> (e & 31)) & 1u; }
@@ -345,6 +412,62 @@ __device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const Row
 #pragma unroll
         for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
         consider<S, INCL>(buf, ctl, c, r, __fmul_rn(r, c.inv_temp), e0 + j, thr);
+    }
+}
+
+// The same three steps for a batch with post-processing: the hot test runs on the raw logits
+// against a raw bound (post_raw_bound), and only a column that passes it pays for the exact value.
+template <class S, bool INCL>
+__device__ __forceinline__ void consider_post(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, int e, float thr) {
+    float l = post_logit(raw, c.post);
+    if (c.pen_bitmap && bm_test(c.bm, e)) l = penalise(l, c.pen);
+    const float v = __fmul_rn(l, c.inv_temp);
+    if (INCL ? v >= thr : v > thr) append<S>(buf, ctl, v, e + c.voff);
+}
+
+// The largest raw logit of one complete vector.
+template <typename T>
+__device__ __forceinline__ float vec_max_raw(const uint4& rawv) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    float m = raw[0];
+#pragma unroll
+    for (int j = 1; j < VEC; j++) m = fmaxf(m, raw[j]);
+    return m;
+}
+
+// The largest raw logit among the columns of one complete vector that carry no penalty.
+template <typename T>
+__device__ __forceinline__ float vec_max_raw_unpenalised(const uint4& rawv, int vec, const RowCtx& c) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    const int e0 = vec * VEC - c.mis;
+    float m = __uint_as_float(0xff800000u);
+#pragma unroll
+    for (int j = 0; j < VEC; j++)
+        if (!(c.pen_bitmap && bm_test(c.bm, e0 + j))) m = fmaxf(m, raw[j]);
+    return m;
+}
+
+template <class S, typename T, bool INCL>
+__device__ __forceinline__ void filter_vec_post(const uint4& rawv, int vec, const RowCtx& c, float rthr, float thr,
+                                                Cand* buf, Ctl* ctl) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    uint32_t pass = 0;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) pass |= (raw[j] >= rthr) ? (1u << j) : 0u;
+    const int e0 = vec * VEC - c.mis;
+    while (pass) {
+        const int j = __ffs(pass) - 1;
+        pass &= pass - 1;
+        float r = raw[0];
+#pragma unroll
+        for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
+        consider_post<S, INCL>(buf, ctl, c, r, e0 + j, thr);
     }
 }
 
@@ -1035,6 +1158,19 @@ __global__ void __launch_bounds__(PENALTY_NT) penalty_rows_kernel(const KArgs a)
 // the stage just freed.  Thread 0 also looks one item ahead: the next item's parameters,
 // history length and history window are in shared memory before the item starts.
 
+// The post-processing alone, in place: what the reference does to the whole logits vector before
+// it samples (simd/runtime.go:258-272; device form native/softmax.cu:963-970).  For callers that
+// want the rewritten logits; the sampler itself applies it on the fly and writes nothing.
+__global__ void __launch_bounds__(256) postprocess_rows_kernel(float* logits, int rows, int vocab, int64_t row_stride,
+                                                               Post post) {
+    const int64_t n = (int64_t)rows * vocab;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / vocab;
+        float* p = logits + r * row_stride + (i - r * vocab);
+        *p = post_logit(*p, post);
+    }
+}
+
 template <typename T, class S>
 struct ItemGeom {
     const uint4* vbase;  // the row rounded down to 16 bytes
@@ -1459,7 +1595,7 @@ struct LdgLayout {
     static constexpr size_t FIXED = 8 * (size_t)S::CAP + 4 * 256 + 512;
 };
 
-template <class S, typename T, int MODE>
+template <class S, typename T, int MODE, bool POST>
 __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KArgs a) {
     constexpr int VEC = Elem<T>::VEC;
     constexpr int NT = S::NT, NWARP = S::NWARP, U = S::U, CAP = S::CAP;
@@ -1488,6 +1624,9 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     c.pen = P.repeat_penalty;
     c.bm = bm;
     c.pen_bitmap = false;
+    c.post.mode = a.post_mode;
+    c.post.scale = a.post_scale;
+    c.post.cap = a.post_cap;
     const uint4* vbase = g.vbase;
     const int a0 = g.a0, b0 = g.b0, elo = g.elo, ehi = g.ehi;
     constexpr int RV = NT * U;  // vectors per region
@@ -1536,6 +1675,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     // ---- stream the item ------------------------------------------------------------------
     const int trig = min(k + max(k >> 1, 16), CAP / 2);  // cut the buffer at this many entries
     float thr = __uint_as_float(0xff800000u);            // -inf
+    float rthr = thr;  // POST: the raw logit every column that can reach thr has at least
 
     if (!careful && nreg > 0) {
         // later regions: the buffer already holds k entries >= thr with lower indices, so an equal
@@ -1548,10 +1688,17 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 mu[u] = __uint_as_float(0x7fc00000u);  // NaN: beyond the item, admitted by no compare
-                if (whole || v0 + u * NT < b0) mu[u] = vec_max_scaled<T>(src[u], c.inv_temp);
+                if (whole || v0 + u * NT < b0)
+                    mu[u] = POST ? vec_max_raw<T>(src[u]) : vec_max_scaled<T>(src[u], c.inv_temp);
                 m = fmaxf(m, mu[u]);
             }
-            if (m > thr) {
+            if (POST) {
+                if (m >= rthr) {
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+                        if (mu[u] >= rthr) filter_vec_post<S, T, false>(src[u], v0 + u * NT, c, rthr, thr, buf, ctl);
+                }
+            } else if (m > thr) {
 #pragma unroll
                 for (int u = 0; u < U; u++)
                     if (mu[u] > thr) filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
@@ -1566,7 +1713,10 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                 } else {
                     bool have;
                     uint32_t kth = refresh_topk<S>(buf, ctl, hist, k, tid, &have);
-                    if (have) thr = key2f(kth);
+                    if (have) {
+                        thr = key2f(kth);
+                        if (POST) rthr = post_raw_bound(thr, c.inv_temp, c.post);
+                    }
                 }
             }
         };
@@ -1578,7 +1728,9 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             float tmax = __uint_as_float(0xff800000u);
 #pragma unroll
             for (int u = 0; u < U; u++)
-                if (v0 + u * NT < b0) tmax = fmaxf(tmax, vec_max_penalised<T>(ra[u], v0 + u * NT, c));
+                if (v0 + u * NT < b0)
+                    tmax = fmaxf(tmax, POST ? vec_max_raw_unpenalised<T>(ra[u], v0 + u * NT, c)
+                                            : vec_max_penalised<T>(ra[u], v0 + u * NT, c));
             float x = tmax;  // bitonic sort across the warp, descending
 #pragma unroll
             for (int k2 = 2; k2 <= 32; k2 <<= 1) {
@@ -1597,10 +1749,19 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             float t0 = ctl->warpv[0];
 #pragma unroll
             for (int w = 1; w < NWARP; w++) t0 = fminf(t0, ctl->warpv[w]);
-            thr = t0;
+            if (POST) {
+                // t0 is a raw logit that k unpenalised columns of this region reach
+                thr = post_seed_value(t0, c.inv_temp, c.post);
+                rthr = post_raw_bound(thr, c.inv_temp, c.post);
 #pragma unroll
-            for (int u = 0; u < U; u++)
-                if (v0 + u * NT < b0) filter_vec<S, T, true>(ra[u], v0 + u * NT, c, thr, buf, ctl);
+                for (int u = 0; u < U; u++)
+                    if (v0 + u * NT < b0) filter_vec_post<S, T, true>(ra[u], v0 + u * NT, c, rthr, thr, buf, ctl);
+            } else {
+                thr = t0;
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (v0 + u * NT < b0) filter_vec<S, T, true>(ra[u], v0 + u * NT, c, thr, buf, ctl);
+            }
         }
         region_end(k + 1);
 
@@ -1634,8 +1795,12 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         if (tid < n1 + n2) {  // at most 4 * VEC columns
             int e = tid < n1 ? r1_lo + tid : r2_lo + (tid - n1);
             float raw = Elem<T>::load1(c.row, e);
-            float v = __fmul_rn(raw, c.inv_temp);
-            if (v >= thr) consider<S, true>(buf, ctl, c, raw, v, e, thr);
+            if (POST) {
+                if (raw >= rthr) consider_post<S, true>(buf, ctl, c, raw, e, thr);
+            } else {
+                float v = __fmul_rn(raw, c.inv_temp);
+                if (v >= thr) consider<S, true>(buf, ctl, c, raw, v, e, thr);
+            }
         }
         __syncthreads();
         if (live_count(ctl) > CAP) careful = true;
@@ -1665,6 +1830,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                 int e = e0 + j * NT + tid;
                 if (e < ehi) {
                     float l = Elem<T>::load1(c.row, e);
+                    if (POST) l = post_logit(l, c.post);
                     if (c.pen_bitmap && bm_test(bm, e)) l = penalise(l, c.pen);
                     float v = __fmul_rn(l, c.inv_temp);
                     if (strict ? (v > thr) : (v >= thr)) append<S>(buf, ctl, v, e + c.voff);
@@ -1774,8 +1940,10 @@ __global__ void __launch_bounds__(WIDE_NT, 1) wide_rows_kernel(const KArgs a) {
     if (pen) build_penalty_bitmap(a, row, wp, hl, nullptr, V, a.vocab_offset, bm, tid, WIDE_NT);
 
     // scaled, penalised value of column e and its key
+    const Post post = {a.post_mode, a.post_scale, a.post_cap};
     auto value = [&](int e) {
         float l = Elem<T>::load1(rowp, e);
+        if (post.mode) l = post_logit(l, post);
         if (pen && bm_test(bm, e)) l = penalise(l, P.repeat_penalty);
         return __fmul_rn(l, inv_temp);
     };
@@ -2208,6 +2376,21 @@ __global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_part
 
 constexpr int kInvalid = (int)cudaErrorInvalidValue;
 
+// The model head's post-processing as the reference gates it (simd/runtime.go:258,264): the
+// multiplier when it is neither 0 nor 1, the soft cap when it is positive.  A negative or
+// non-finite multiplier and an infinite cap are refused.
+bool post_ok(float scale, float cap) {
+    if (!(scale == scale) || std::isinf(scale) || scale < 0.0f) return false;
+    if (std::isinf(cap)) return false;
+    return true;
+}
+int post_mode_of(float scale, float cap, uint32_t flags) {
+    int m = 0;
+    if (scale != 0.0f && scale != 1.0f) m |= POST_SCALE;
+    if (cap > 0.0f) m |= POST_CAP | ((flags & MANTLE_SAMPLE_SOFTCAP_TANHF) ? POST_TANHF : 0);
+    return m;
+}
+
 bool batch_ok(const MantleSampleBatch* b, bool need_outputs) {
     if (!b || !b->logits || b->rows <= 0 || b->vocab <= 0) return false;
     if (b->vocab > MANTLE_SAMPLE_MAX_VOCAB) return false;
@@ -2216,7 +2399,13 @@ bool batch_ok(const MantleSampleBatch* b, bool need_outputs) {
     if (b->hist_stride < 0 || b->n_exclude < 0) return false;
     if (b->n_exclude > 0 && !b->exclude) return false;
     if (b->splits < 0 || b->reserved != 0) return false;
-    if (b->flags & ~(MANTLE_SAMPLE_WRITE_BACK_PENALTY | MANTLE_SAMPLE_PENALTY_PREAPPLIED)) return false;
+    if (b->flags & ~(MANTLE_SAMPLE_WRITE_BACK_PENALTY | MANTLE_SAMPLE_PENALTY_PREAPPLIED | MANTLE_SAMPLE_SOFTCAP_TANHF))
+        return false;
+    if (!post_ok(b->logit_scale, b->logit_softcap)) return false;
+    // the fused post-processing leaves the logits as they are: nothing to write back, nothing pre-applied
+    if (post_mode_of(b->logit_scale, b->logit_softcap, b->flags) &&
+        (b->flags & (MANTLE_SAMPLE_WRITE_BACK_PENALTY | MANTLE_SAMPLE_PENALTY_PREAPPLIED)))
+        return false;
     if ((b->flags & MANTLE_SAMPLE_WRITE_BACK_PENALTY) && b->dtype != MANTLE_DTYPE_F32) return false;
     const size_t esz = b->dtype == MANTLE_DTYPE_F32 ? 4 : 2;
     if (reinterpret_cast<uintptr_t>(b->logits) % esz) return false;
@@ -2254,6 +2443,17 @@ int forced_kernel() {
 bool use_small_shape(int max_top_k) {
     if (max_top_k > ShapeSmallK::KCAP) return false;
     return forced_shape() != 2;
+}
+
+// Which streaming kernel serves a batch.  Plain loads for shortlists of at most 256 entries
+// (measured on the 4096 x 151 936 batch: 0.442 ms against 0.541 ms for the bulk-copy ring) and
+// for every batch with fused post-processing, which only that kernel implements; the ring
+// for longer shortlists.  MANTLE_SAMPLER_KERNEL=ldg|tma overrides the choice where both can serve.
+bool use_ldg(int max_top_k, bool post) {
+    if (post) return true;
+    if (forced_kernel() == 2) return false;
+    if (forced_kernel() == 1) return true;
+    return max_top_k <= ShapeLdg::KCAP;
 }
 
 bool use_alt_shape(int max_top_k) { return forced_shape() == 3 && max_top_k <= ShapeAlt::KCAP; }
@@ -2299,11 +2499,12 @@ int choose_splits(const MantleSampleBatch* b) {
     if (b->max_top_k > KMAX) return 1;  // long shortlists: one CTA per row, no merge
     const int vec = b->dtype == MANTLE_DTYPE_F32 ? 4 : 8;
     const int nvec = (b->vocab + vec - 1) / vec + 1;
-    const bool small = use_small_shape(b->max_top_k);
-    const bool ldg = forced_kernel() != 2 && b->max_top_k <= ShapeLdg::KCAP;
-    const int chunk = ldg ? ShapeLdg::NT * ShapeLdg::U
+    const bool ldg = use_ldg(b->max_top_k, post_mode_of(b->logit_scale, b->logit_softcap, b->flags) != 0);
+    const bool small = ldg ? b->max_top_k <= ShapeLdg::KCAP : use_small_shape(b->max_top_k);
+    const int chunk = ldg ? (small ? ShapeLdg::NT * ShapeLdg::U : ShapeLdgLargeK::NT * ShapeLdgLargeK::U)
                           : (small ? ShapeSmallK::NT * ShapeSmallK::U : ShapeLargeK::NT * ShapeLargeK::U);
-    const int per_sm = ldg ? ShapeLdg::MINB : (small ? ShapeSmallK::MINB : ShapeLargeK::MINB);
+    const int per_sm = ldg ? (small ? ShapeLdg::MINB : ShapeLdgLargeK::MINB)
+                           : (small ? ShapeSmallK::MINB : ShapeLargeK::MINB);
     const int max_by_k = MERGE_CAP / b->max_top_k;  // the merge holds splits * k candidates
     if (b->splits > 0) return std::max(1, std::min(std::min(b->splits, max_by_k), std::min(nvec, 64)));
     const int max_by_work = nvec / (2 * chunk);  // at least two chunks per CTA
@@ -2342,6 +2543,9 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
     a.part_cap = 0;
     a.parts = 0;
     a.hist_tma_ok = a.history && reinterpret_cast<uintptr_t>(a.history) % 16 == 0 && a.hist_stride % 4 == 0;
+    a.post_mode = post_mode_of(b->logit_scale, b->logit_softcap, b->flags);
+    a.post_scale = b->logit_scale;
+    a.post_cap = b->logit_softcap;
 #ifdef MANTLE_DEBUG_SWITCHES
     const char* dbg = getenv("MANTLE_SAMPLER_DEBUG");
     a.debug = dbg ? atoi(dbg) : 0;
@@ -2372,31 +2576,33 @@ int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
     return (int)cudaGetLastError();
 }
 
-template <int MODE>
-int launch_scan_ldg(const KArgs& a, int dtype, cudaStream_t stream) {
-    using S = ShapeLdg;
+template <class S, typename T, int MODE, bool POST>
+int launch_scan_ldg_as(const KArgs& a, cudaStream_t stream) {
     const size_t smem = LdgLayout<S>::FIXED + bitmap_words(a.vocab) * sizeof(uint32_t);
     const long long items = (long long)a.rows * a.splits;
     if (items > 0x7fffffffLL) return kInvalid;
-    cudaError_t e;
-    if (dtype == MANTLE_DTYPE_F32) {
-        auto kern = scan_rows_ldg_kernel<S, float, MODE>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        kern<<<(int)items, S::NT, smem, stream>>>(a);
-    } else {
-        auto kern = scan_rows_ldg_kernel<S, bf16_t, MODE>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        kern<<<(int)items, S::NT, smem, stream>>>(a);
-    }
+    auto kern = scan_rows_ldg_kernel<S, T, MODE, POST>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<(int)items, S::NT, smem, stream>>>(a);
     return (int)cudaGetLastError();
+}
+
+template <class S, int MODE>
+int launch_scan_ldg(const KArgs& a, int dtype, cudaStream_t stream) {
+    if (a.post_mode)
+        return dtype == MANTLE_DTYPE_F32 ? launch_scan_ldg_as<S, float, MODE, true>(a, stream)
+                                         : launch_scan_ldg_as<S, bf16_t, MODE, true>(a, stream);
+    return dtype == MANTLE_DTYPE_F32 ? launch_scan_ldg_as<S, float, MODE, false>(a, stream)
+                                     : launch_scan_ldg_as<S, bf16_t, MODE, false>(a, stream);
 }
 
 template <int MODE>
 int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
-    // Measured on the 4096 x 151 936 batch: plain loads 0.453 ms, bulk-copy ring 0.541 ms.
-    if (forced_kernel() != 2 && a.max_top_k <= ShapeLdg::KCAP) return launch_scan_ldg<MODE>(a, dtype, stream);
+    if (use_ldg(a.max_top_k, a.post_mode != 0)) {
+        if (a.max_top_k <= ShapeLdg::KCAP) return launch_scan_ldg<ShapeLdg, MODE>(a, dtype, stream);
+        return launch_scan_ldg<ShapeLdgLargeK, MODE>(a, dtype, stream);
+    }
     if (use_alt_shape(a.max_top_k)) return launch_scan_shape<ShapeAlt, MODE>(a, dtype, stream);
     if (use_small_shape(a.max_top_k)) return launch_scan_shape<ShapeSmallK, MODE>(a, dtype, stream);
     return launch_scan_shape<ShapeLargeK, MODE>(a, dtype, stream);
@@ -2450,7 +2656,7 @@ size_t parts_bytes(int rows, int parts, int cap) {
 
 }  // namespace
 
-extern "C" int mantleCudaSamplerAbiVersion(void) { return 1; }
+extern "C" int mantleCudaSamplerAbiVersion(void) { return 2; }
 
 extern "C" int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* splits) {
     if (!splits || !batch_ok(batch, true)) return kInvalid;
@@ -2498,6 +2704,20 @@ extern "C" int mantleCudaRepeatPenaltyRowsF32(const MantleSampleBatch* batch, ma
     KArgs a;
     fill_args(a, batch);
     return launch_penalty(a, static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int mantleCudaLogitPostprocessRowsF32(float* logits, int rows, int vocab, int64_t row_stride,
+                                                float logit_scale, float logit_softcap, uint32_t flags,
+                                                mantleCudaStream_t stream_) {
+    if (!logits || rows <= 0 || vocab <= 0 || row_stride < vocab) return kInvalid;
+    if (reinterpret_cast<uintptr_t>(logits) % 4 || (flags & ~MANTLE_SAMPLE_SOFTCAP_TANHF)) return kInvalid;
+    if (!post_ok(logit_scale, logit_softcap)) return kInvalid;
+    Post post = {post_mode_of(logit_scale, logit_softcap, flags), logit_scale, logit_softcap};
+    if (!post.mode) return 0;
+    const long long n = (long long)rows * vocab;
+    const int grid = (int)std::min<long long>((n + 255) / 256, (long long)smem_budget().sms * 32);
+    postprocess_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_)>>>(logits, rows, vocab, row_stride, post);
+    return (int)cudaGetLastError();
 }
 
 extern "C" int mantleCudaArgMaxRowsF32(const float* x, int rows, int n, int64_t row_stride, int* out_idx,

@@ -16,6 +16,7 @@ MAX_TOP_K = 1024
 MAX_VOCAB = 1 << 20
 FLAG_WRITE_BACK_PENALTY = 1
 FLAG_PENALTY_PREAPPLIED = 2
+FLAG_SOFTCAP_TANHF = 4
 STATUS_TOPK_RANGE = 1
 STATUS_EMPTY = 2
 STATUS_TIMEOUT = 4
@@ -65,6 +66,8 @@ class SampleBatch(C.Structure):
         ("splits", C.c_int32),
         ("flags", C.c_uint32),
         ("reserved", C.c_uint32),
+        ("logit_scale", C.c_float),
+        ("logit_softcap", C.c_float),
     ]
 
 
@@ -74,6 +77,10 @@ EXPORTS = {
     "mantleCudaSamplerWorkspaceBytes": (C.c_int, [C.POINTER(SampleBatch), C.POINTER(C.c_size_t)]),
     "mantleCudaSamplerSplits": (C.c_int, [C.POINTER(SampleBatch), C.POINTER(C.c_int)]),
     "mantleCudaRepeatPenaltyRowsF32": (C.c_int, [C.POINTER(SampleBatch), C.c_void_p]),
+    "mantleCudaLogitPostprocessRowsF32": (
+        C.c_int,
+        [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_float, C.c_float, C.c_uint32, C.c_void_p],
+    ),
     "mantleCudaArgMaxRowsF32": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_void_p]),
     "mantleCudaSampleLocalTopK": (
         C.c_int,
@@ -158,7 +165,7 @@ def load():
         f = getattr(L, name)  # AttributeError here means the build is broken: do not hide it
         f.restype = res
         f.argtypes = args
-    if L.mantleCudaSamplerAbiVersion() != 1:
+    if L.mantleCudaSamplerAbiVersion() != 2:
         raise RuntimeError("CUDA sampler library ABI mismatch")
     _lib = L
     return L

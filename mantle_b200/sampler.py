@@ -78,10 +78,12 @@ class BatchPlan:
     params   uint8 CUDA tensor of rows*40 bytes (params_to_device)
     history  optional [rows, H] int32 CUDA tensor, oldest id first; hist_len optional [rows] int32
     exclude  optional [E] int32 CUDA tensor (stop tokens)
+    logit_scale, logit_softcap   the model head's multiplier and soft cap (simd/runtime.go:258-272),
+             applied on the fly; 0 switches either off
     """
 
     def __init__(self, logits, params, max_top_k, history=None, hist_len=None, exclude=None, vocab=None,
-                 cand_cap=0, want_counts=True, flags=0, splits=0):
+                 cand_cap=0, want_counts=True, flags=0, splits=0, logit_scale=0.0, logit_softcap=0.0):
         self.lib = native.load()
         if not logits.is_cuda or logits.dim() != 2 or logits.stride(1) != 1:
             raise ValueError("logits must be a 2-D CUDA tensor with unit column stride")
@@ -133,6 +135,8 @@ class BatchPlan:
         b.status = out.status.data_ptr()
         b.splits = splits
         b.flags = flags
+        b.logit_scale = logit_scale
+        b.logit_softcap = logit_softcap
         self.batch = b
         nbytes = C.c_size_t(0)
         native.check(self.lib.mantleCudaSamplerWorkspaceBytes(C.byref(b), C.byref(nbytes)), "WorkspaceBytes")
@@ -156,6 +160,20 @@ def sample_rows(logits, params, max_top_k, **kw):
     """One-shot form of BatchPlan: sample every row, return the outputs (device tensors)."""
     with torch.cuda.device(logits.device):
         return BatchPlan(logits, params, max_top_k, **kw).launch()
+
+
+def logit_postprocess_rows_(logits, logit_scale=0.0, logit_softcap=0.0, flags=0, stream=None):
+    """The model head's multiplier and soft cap alone, in place on float32 rows
+    (simd/runtime.go:258-272; device form native/softmax.cu:963-970)."""
+    lib = native.load()
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("logits must be a 2-D float32 CUDA tensor with unit column stride")
+    with torch.cuda.device(logits.device):
+        rc = lib.mantleCudaLogitPostprocessRowsF32(logits.data_ptr(), logits.shape[0], logits.shape[1],
+                                                   logits.stride(0), logit_scale, logit_softcap, flags,
+                                                   _stream_ptr(stream))
+    native.check(rc, "mantleCudaLogitPostprocessRowsF32")
+    return logits
 
 
 def repeat_penalty_rows_(logits, params, history, hist_len=None, exclude=None, stream=None):
@@ -191,7 +209,7 @@ def argmax_rows(x, stream=None):
 
 
 def local_topk(logits, params, max_top_k, vocab_offset, vocab_total, history=None, hist_len=None, exclude=None,
-               part_cap=None, stream=None):
+               part_cap=None, stream=None, logit_scale=0.0, logit_softcap=0.0, flags=0):
     """Vocabulary-sharded step 1: this GPU's shortlist with global ids.  Returns (val, idx, cnt)."""
     lib = native.load()
     rows = logits.shape[0]
@@ -216,6 +234,9 @@ def local_topk(logits, params, max_top_k, vocab_offset, vocab_total, history=Non
         b.exclude = exclude.data_ptr()
         b.n_exclude = exclude.numel()
     b.params = params.data_ptr()
+    b.flags = flags
+    b.logit_scale = logit_scale
+    b.logit_softcap = logit_softcap
     with torch.cuda.device(dev):
         rc = lib.mantleCudaSampleLocalTopK(C.byref(b), vocab_offset, vocab_total, _ptr(val), _ptr(idx), _ptr(cnt), cap,
                                            _stream_ptr(stream))

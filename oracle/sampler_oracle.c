@@ -50,6 +50,27 @@ float mantle_oracle_fast_exp(float x) {
     return poly * scale;
 }
 
+/* internal/backend/simd/ops.go:165-175 -- fastTanh, built on the same fastExp
+ * (simd/ops.go:111-150 is a copy of sampler.go:10-31). */
+float mantle_oracle_fast_tanh(float x) {
+    if (x > 10.0f) return 1.0f;
+    if (x < -10.0f) return -1.0f;
+    float e2x = mantle_oracle_fast_exp(2.0f * x);
+    return (e2x - 1.0f) / (e2x + 1.0f);
+}
+
+/* internal/backend/simd/runtime.go:258-272 -- what the model head does to the logits before
+ * they reach the sampler, in place: the LMHeadMultiplier loop (when the multiplier is
+ * neither 0 nor 1), then the FinalLogitSoftcap loop of the host path (when the cap is
+ * positive).  Pinned only loosely by the reference's tests: the cap is the identity when it
+ * is not positive and damps large logits (internal/backend/cuda/graph_test.go:255-263). */
+void mantle_oracle_postprocess(float *logits, int64_t n, float scale, float softcap) {
+    if (scale != 0.0f && scale != 1.0f)
+        for (int64_t i = 0; i < n; i++) logits[i] *= scale;
+    if (softcap > 0.0f)
+        for (int64_t i = 0; i < n; i++) logits[i] = mantle_oracle_fast_tanh(logits[i] / softcap) * softcap;
+}
+
 /* sampler.go:61-83 -- NewSampler's normalisation; the seed stays with the host RNG. */
 void mantle_oracle_normalize_config(const MantleSamplerConfig *cfg, MantleSampleParams *out) {
     memset(out, 0, sizeof *out);

@@ -13,7 +13,7 @@ def to_bf16_bits(t):
 
 
 def run_gpu(logits, params, max_top_k, history=None, hist_len=None, exclude=None, cand_cap=0, flags=0, splits=0,
-            vocab=None):
+            vocab=None, logit_scale=0.0, logit_softcap=0.0):
     """logits: CUDA tensor.  Returns dict of numpy arrays plus the plan."""
     dev = logits.device
     p_dev = sampler.params_to_device(params, dev)
@@ -22,7 +22,8 @@ def run_gpu(logits, params, max_top_k, history=None, hist_len=None, exclude=None
     ex_dev = None if exclude is None else torch.as_tensor(np.ascontiguousarray(exclude, dtype=np.int32)).to(dev)
     with torch.cuda.device(dev):
         plan = sampler.BatchPlan(logits, p_dev, max_top_k, history=h_dev, hist_len=hl_dev, exclude=ex_dev,
-                                 cand_cap=cand_cap, flags=flags, splits=splits, vocab=vocab)
+                                 cand_cap=cand_cap, flags=flags, splits=splits, vocab=vocab,
+                                 logit_scale=logit_scale, logit_softcap=logit_softcap)
         out = plan.launch()
         torch.cuda.synchronize(dev)
     res = dict(
@@ -57,17 +58,30 @@ def compare(gpu, ref, cand_cap=0, exact_prob=True, where=""):
             assert np.all(np.abs(a32 - b32) <= 1e-5 * np.abs(b32)), (where, r)
 
 
+def widen_bf16(bits):
+    """uint16 bfloat16 bit patterns -> the float32 values they stand for (exact)."""
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
 def check_against_oracle(logits_np, params, max_top_k, history=None, hist_len=None, exclude=None, cand_cap=0,
-                         flags=0, splits=0, device="cuda:0", where="", bf16=False):
-    """logits_np: float32 [rows, V] host array (or uint16 bf16 bits when bf16=True)."""
+                         flags=0, splits=0, device="cuda:0", where="", bf16=False, logit_scale=0.0,
+                         logit_softcap=0.0, exact_prob=True):
+    """logits_np: float32 [rows, V] host array (or uint16 bf16 bits when bf16=True).  With a
+    multiplier or soft cap the oracle rewrites its copy of the logits first, as the reference's
+    model head does, and the GPU applies the same arithmetic on the fly."""
     if bf16:
         dev_logits = torch.from_numpy(logits_np.view(np.int16).copy()).to(device).view(torch.bfloat16)
     else:
         dev_logits = torch.from_numpy(logits_np.copy()).to(device)
-    gpu = run_gpu(dev_logits, params, max_top_k, history, hist_len, exclude, cand_cap, flags, splits)
+    gpu = run_gpu(dev_logits, params, max_top_k, history, hist_len, exclude, cand_cap, flags, splits,
+                  logit_scale=logit_scale, logit_softcap=logit_softcap)
     ref_logits = logits_np.copy()
+    if logit_scale or logit_softcap:
+        if bf16:
+            ref_logits = np.ascontiguousarray(widen_bf16(ref_logits))
+        O.postprocess(ref_logits, logit_scale, logit_softcap)
     ref = O.sample_rows(ref_logits, params, history=history, hist_len=hist_len, exclude=exclude, cand_cap=cand_cap)
-    compare(gpu, ref, cand_cap, where=where)
+    compare(gpu, ref, cand_cap, exact_prob=exact_prob, where=where)
     assert gpu["status"] == 0, where
     if flags & native.FLAG_WRITE_BACK_PENALTY:
         assert np.array_equal(dev_logits.cpu().numpy(), ref_logits), where  # the in-place side effect

@@ -54,6 +54,10 @@ def lib():
         L = C.CDLL(ORACLE_SO)
         L.mantle_oracle_fast_exp.restype = C.c_float
         L.mantle_oracle_fast_exp.argtypes = [C.c_float]
+        L.mantle_oracle_fast_tanh.restype = C.c_float
+        L.mantle_oracle_fast_tanh.argtypes = [C.c_float]
+        L.mantle_oracle_postprocess.restype = None
+        L.mantle_oracle_postprocess.argtypes = [C.c_void_p, C.c_int64, C.c_float, C.c_float]
         L.mantle_oracle_normalize_config.restype = None
         L.mantle_oracle_normalize_config.argtypes = [C.c_void_p, C.c_void_p]
         L.mantle_oracle_can_use_device_greedy.restype = C.c_int
@@ -84,6 +88,17 @@ def _ptr(a):
 
 def fast_exp(x):
     return float(np.float32(lib().mantle_oracle_fast_exp(C.c_float(float(np.float32(x))))))
+
+
+def fast_tanh(x):
+    return float(lib().mantle_oracle_fast_tanh(C.c_float(x)))
+
+
+def postprocess(logits, scale=0.0, softcap=0.0):
+    """The model head's multiplier and soft cap, in place on a contiguous float32 array."""
+    assert logits.dtype == np.float32 and logits.flags.c_contiguous
+    lib().mantle_oracle_postprocess(_ptr(logits), logits.size, C.c_float(scale), C.c_float(softcap))
+    return logits
 
 
 def normalize(seed=0, temperature=0.0, top_k=0, top_p=0.0, min_p=0.0, repeat_penalty=0.0, repeat_last_n=0,

@@ -24,13 +24,13 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), n
         assert n in native.EXPORTS, "binding missing for " + n
-    assert lib.mantleCudaSamplerAbiVersion() == 1
+    assert lib.mantleCudaSamplerAbiVersion() == 2
 
 
 def test_struct_layout_matches_header():
     assert native.PARAMS_DTYPE.itemsize == 40
     assert native.PARAMS_DTYPE.fields["uniform"][1] == 32
-    assert C.sizeof(native.SampleBatch) == 136
+    assert C.sizeof(native.SampleBatch) == 144
     assert native.SampleBatch.row_stride.offset == 24
     assert native.SampleBatch.cand_stride.offset == 120
 
@@ -57,6 +57,8 @@ def test_invalid_arguments_are_rejected_on_the_host():
         ("logits", 0), ("rows", 0), ("vocab", 0), ("vocab", native.MAX_VOCAB + 1), ("dtype", 7),
         ("row_stride", 999), ("max_top_k", 0), ("max_top_k", native.MAX_VOCAB + 1), ("params", 0), ("next", 0),
         ("n_exclude", 3), ("hist_stride", -1), ("flags", 8), ("reserved", 1), ("splits", -1), ("logits", 0x1001),
+        ("logit_scale", -2.0), ("logit_scale", float("nan")), ("logit_scale", float("inf")),
+        ("logit_softcap", float("inf")),
     ]
     for field, value in mutations:
         b = good_batch()
@@ -73,6 +75,14 @@ def test_invalid_arguments_are_rejected_on_the_host():
     b.dtype = native.DTYPE_BF16
     b.flags = native.FLAG_WRITE_BACK_PENALTY  # bf16 rows cannot hold the penalised value
     assert lib.mantleCudaSampleRows(C.byref(b), None, 0, None) == inv
+    for flag in (native.FLAG_WRITE_BACK_PENALTY, native.FLAG_PENALTY_PREAPPLIED):
+        b = good_batch()
+        b.logit_softcap, b.flags = 30.0, flag  # fused post-processing never rewrites the logits
+        assert lib.mantleCudaSampleRows(C.byref(b), None, 0, None) == inv
+    assert lib.mantleCudaLogitPostprocessRowsF32(None, 1, 10, 10, 1.0, 30.0, 0, None) == inv
+    assert lib.mantleCudaLogitPostprocessRowsF32(0x10, 1, 10, 5, 1.0, 30.0, 0, None) == inv
+    assert lib.mantleCudaLogitPostprocessRowsF32(0x10, 1, 10, 10, -1.0, 30.0, 0, None) == inv
+    assert lib.mantleCudaLogitPostprocessRowsF32(0x10, 1, 10, 10, 1.0, 30.0, 1, None) == inv
     b = good_batch()
     b.rows, b.splits = 1, 4  # split rows need a workspace
     assert lib.mantleCudaSampleRows(C.byref(b), None, 0, None) == inv

@@ -232,3 +232,31 @@ def test_batch_driver_threads_agree():
     b = O.sample_rows(logits.copy(), params, threads=4)
     assert a["threads"] == 1 and b["threads"] == 4
     assert np.array_equal(a["next"], b["next"])
+
+
+# ---- the model head's post-processing (simd/runtime.go:258-272, simd/ops.go:165-175) --------------
+
+def test_postprocess_properties_the_reference_tests_hold():
+    """internal/backend/cuda/graph_test.go:255-263: a cap that is not positive is the identity;
+    a large logit is damped to something positive below itself.  Plus the gates of the
+    multiplier (0 and 1 leave the logits alone) and the saturation points of fastTanh."""
+    x = np.array([1.0, 100.0, -3.0, 0.0], dtype=np.float32)
+    assert np.array_equal(O.postprocess(x.copy(), 0.0, 0.0), x)
+    assert np.array_equal(O.postprocess(x.copy(), 1.0, -5.0), x)
+    y = O.postprocess(x.copy(), 0.0, 30.0)
+    assert 0.0 < y[1] < 30.0 and abs(y[1] - 30.0 * np.tanh(100.0 / 30.0)) < 1e-3
+    assert np.array_equal(O.postprocess(x.copy(), 2.0, 0.0), x * np.float32(2.0))
+    assert O.fast_tanh(10.5) == 1.0 and O.fast_tanh(-10.5) == -1.0 and O.fast_tanh(0.0) == 0.0
+    # fastTanh built on fastExp: (e - 1) / (e + 1) in float32
+    for v in (0.3, -0.3, 2.5, 9.99):
+        e = np.float32(O.fast_exp(float(np.float32(2.0) * np.float32(v))))
+        assert O.fast_tanh(v) == float((e - np.float32(1.0)) / (e + np.float32(1.0)))
+
+
+def test_fast_tanh_error_bound():
+    """The streaming kernel's raw-logit filter relies on |fastTanh - tanh| < 1e-5 (it allows for
+    several times that); sampled here, the exhaustive figure over [-10, 10] is 1.7e-6."""
+    rng = np.random.default_rng(3)
+    xs = np.concatenate([rng.uniform(-10, 10, 200000), rng.uniform(-0.5, 0.5, 100000)]).astype(np.float32)
+    got = O.postprocess(xs.copy(), 0.0, 1.0)
+    assert np.max(np.abs(got.astype(np.float64) - np.tanh(xs.astype(np.float64)))) < 3e-6
