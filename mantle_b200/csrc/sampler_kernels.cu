@@ -136,6 +136,13 @@ struct Pre {
 };
 static_assert(sizeof(Pre) <= 256, "prefetch block outgrew its slot");
 
+// Post-processing of the model head's output, applied to every logit before the sampler sees
+// it: POST_SCALE l *= scale; POST_CAP l = tanh(l / cap) * cap (POST_TANHF picks tanhf).
+struct Post {
+    int mode;
+    float scale, cap;
+};
+
 struct KArgs {
     const void* logits;
     int64_t row_stride;
@@ -166,11 +173,7 @@ struct KArgs {
     int part_cap;
     int parts;
     int hist_tma_ok;  // history base 16-byte aligned and hist_stride a multiple of 4
-    // post-processing of the model head's output, applied to every logit before the sampler
-    // sees it: POST_SCALE l *= post_scale; POST_CAP l = tanh(l / post_cap) * post_cap
-    int post_mode;
-    float post_scale;
-    float post_cap;
+    Post post;  // read from the kernel's parameter space where it is used, never copied to registers
 #ifdef MANTLE_DEBUG_SWITCHES
     int debug;
 #endif
@@ -233,10 +236,6 @@ __device__ __forceinline__ float fast_tanh(float x) {
 // What the model head does to a logit before the sampler sees it (simd/runtime.go:258-272):
 // the multiplier first, then the soft cap, with the host path's fastTanh or, on request, with
 // tanhf as the reference's device kernel has it (native/softmax.cu:963-970).
-struct Post {
-    int mode;
-    float scale, cap;
-};
 __device__ __forceinline__ float post_logit(float l, const Post& p) {
     if (p.mode & POST_SCALE) l = __fmul_rn(l, p.scale);
     if (p.mode & POST_CAP) {
@@ -276,6 +275,7 @@ __device__ __forceinline__ float post_seed_value(float raw0, float inv_temp, con
     const float ninf = __uint_as_float(0xff800000u);
     if (!(raw0 > ninf)) return ninf;
     const float v0 = __fmul_rn(post_logit(raw0, p), inv_temp);
+    if (!(fabsf(v0) < 3.0e38f)) return v0;  // an infinite value is its own bound
     const float slack = (p.mode & POST_CAP) ? 4.0f * POST_EPS * p.cap * inv_temp : 0.0f;
     return v0 - slack - fabsf(v0) * 1e-5f;
 }
@@ -327,7 +327,6 @@ struct RowCtx {
     float pen;
     bool pen_bitmap;      // the penalty is applied from the bitmap (logits stay read-only)
     const uint32_t* bm;   // bitmap, bit e set: column e is penalised
-    Post post;            // only read by the kernels built with POST
 };
 
 __device__ __forceinline__ bool bm_test(const uint32_t* bm, int e) { return (bm[e >> 5] >> (e & 31)) & 1u; }
@@ -351,11 +350,22 @@ __device__ __forceinline__ void append(Cand* buf, Ctl* ctl, float v, int gidx) {
 // logit (l/p < l for l > 0, l*p < l for l < 0, p > 1), so filtering raw values first is
 // conservative: only here, on the rare survivor, is the bitmap consulted, the penalty
 // applied and the filter repeated on the true value.
+// A survivor that carries a penalty is rarer still (a column of the history window among the few
+// that pass the filter); its divide lives out of line, once per kernel, so that the streaming
+// loop stays small.  The candidate buffer and the control block sit at fixed offsets.
+template <class S>
+__device__ __noinline__ void penalised_survivor(float raw, int gidx, float thr, bool incl, float inv_temp, float pen) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + 8 * (size_t)S::CAP + 4 * 256);
+    const float v = __fmul_rn(penalise(raw, pen), inv_temp);
+    if (incl ? v >= thr : v > thr) append<S>(buf, ctl, v, gidx);
+}
 template <class S, bool INCL>
 __device__ __forceinline__ void consider(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, float v, int e, float thr) {
     if (c.pen_bitmap && bm_test(c.bm, e)) {
-        v = __fmul_rn(penalise(raw, c.pen), c.inv_temp);
-        if (!(INCL ? v >= thr : v > thr)) return;
+        penalised_survivor<S>(raw, e + c.voff, thr, INCL, c.inv_temp, c.pen);
+        return;
     }
     append<S>(buf, ctl, v, e + c.voff);
 }
@@ -417,12 +427,28 @@ __device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const Row
 
 // The same three steps for a batch with post-processing: the hot test runs on the raw logits
 // against a raw bound (post_raw_bound), and only a column that passes it pays for the exact value.
+// The exact value of a survivor is a few hundred instructions (two divides, fastExp or tanhf).
+// Inlined at every place a survivor can turn up it made the streaming loop too large for the
+// instruction cache (measured: as many stalls waiting for instructions as at barriers), so it
+// exists once per kernel, out of line, with everything it needs passed by value; the candidate
+// buffer and the control block sit at fixed offsets of the CTA's shared memory.
+template <class S>
+__device__ __noinline__ void post_survivor(float raw, int e, float thr, bool incl, float inv_temp, float pen,
+                                           int voff, int mode, float scale, float cap) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + 8 * (size_t)S::CAP + 4 * 256);
+    const Post post = {mode, scale, cap};
+    float l = post_logit(raw, post);
+    if (pen != 0.0f) l = penalise(l, pen);  // 0: this column carries no penalty
+    const float v = __fmul_rn(l, inv_temp);
+    if (incl ? v >= thr : v > thr) append<S>(buf, ctl, v, e + voff);
+}
 template <class S, bool INCL>
-__device__ __forceinline__ void consider_post(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, int e, float thr) {
-    float l = post_logit(raw, c.post);
-    if (c.pen_bitmap && bm_test(c.bm, e)) l = penalise(l, c.pen);
-    const float v = __fmul_rn(l, c.inv_temp);
-    if (INCL ? v >= thr : v > thr) append<S>(buf, ctl, v, e + c.voff);
+__device__ __forceinline__ void consider_post(Cand* buf, Ctl* ctl, const RowCtx& c, const Post& post, float raw,
+                                              int e, float thr) {
+    post_survivor<S>(raw, e, thr, INCL, c.inv_temp, (c.pen_bitmap && bm_test(c.bm, e)) ? c.pen : 0.0f, c.voff,
+                     post.mode, post.scale, post.cap);
 }
 
 // The largest raw logit of one complete vector.
@@ -452,8 +478,8 @@ __device__ __forceinline__ float vec_max_raw_unpenalised(const uint4& rawv, int 
 }
 
 template <class S, typename T, bool INCL>
-__device__ __forceinline__ void filter_vec_post(const uint4& rawv, int vec, const RowCtx& c, float rthr, float thr,
-                                                Cand* buf, Ctl* ctl) {
+__device__ __forceinline__ void filter_vec_post(const uint4& rawv, int vec, const RowCtx& c, const Post& post,
+                                                float rthr, float thr, Cand* buf, Ctl* ctl) {
     constexpr int VEC = Elem<T>::VEC;
     float raw[VEC];
     Elem<T>::widen(rawv, raw);
@@ -467,7 +493,7 @@ __device__ __forceinline__ void filter_vec_post(const uint4& rawv, int vec, cons
         float r = raw[0];
 #pragma unroll
         for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
-        consider_post<S, INCL>(buf, ctl, c, r, e0 + j, thr);
+        consider_post<S, INCL>(buf, ctl, c, post, r, e0 + j, thr);
     }
 }
 
@@ -1624,9 +1650,6 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     c.pen = P.repeat_penalty;
     c.bm = bm;
     c.pen_bitmap = false;
-    c.post.mode = a.post_mode;
-    c.post.scale = a.post_scale;
-    c.post.cap = a.post_cap;
     const uint4* vbase = g.vbase;
     const int a0 = g.a0, b0 = g.b0, elo = g.elo, ehi = g.ehi;
     constexpr int RV = NT * U;  // vectors per region
@@ -1639,6 +1662,8 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
 #pragma unroll
         for (int u = 0; u < U; u++) {
             int v = a0 + r * RV + u * NT + tid;
+            // the zero fill is not read (the tests below mask what lies beyond the item), but a load
+            // that kept the register's old value would have to wait for its last reader (measured: 1.6 % slower)
             dst[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
         }
     };
@@ -1676,6 +1701,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     const int trig = min(k + max(k >> 1, 16), CAP / 2);  // cut the buffer at this many entries
     float thr = __uint_as_float(0xff800000u);            // -inf
     float rthr = thr;  // POST: the raw logit every column that can reach thr has at least
+    const Post& POSTP = a.post;
 
     if (!careful && nreg > 0) {
         // later regions: the buffer already holds k entries >= thr with lower indices, so an equal
@@ -1696,7 +1722,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                 if (m >= rthr) {
 #pragma unroll
                     for (int u = 0; u < U; u++)
-                        if (mu[u] >= rthr) filter_vec_post<S, T, false>(src[u], v0 + u * NT, c, rthr, thr, buf, ctl);
+                        if (mu[u] >= rthr) filter_vec_post<S, T, false>(src[u], v0 + u * NT, c, POSTP, rthr, thr, buf, ctl);
                 }
             } else if (m > thr) {
 #pragma unroll
@@ -1715,7 +1741,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                     uint32_t kth = refresh_topk<S>(buf, ctl, hist, k, tid, &have);
                     if (have) {
                         thr = key2f(kth);
-                        if (POST) rthr = post_raw_bound(thr, c.inv_temp, c.post);
+                        if (POST) rthr = post_raw_bound(thr, c.inv_temp, POSTP);
                     }
                 }
             }
@@ -1751,11 +1777,11 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             for (int w = 1; w < NWARP; w++) t0 = fminf(t0, ctl->warpv[w]);
             if (POST) {
                 // t0 is a raw logit that k unpenalised columns of this region reach
-                thr = post_seed_value(t0, c.inv_temp, c.post);
-                rthr = post_raw_bound(thr, c.inv_temp, c.post);
+                thr = post_seed_value(t0, c.inv_temp, POSTP);
+                rthr = post_raw_bound(thr, c.inv_temp, POSTP);
 #pragma unroll
                 for (int u = 0; u < U; u++)
-                    if (v0 + u * NT < b0) filter_vec_post<S, T, true>(ra[u], v0 + u * NT, c, rthr, thr, buf, ctl);
+                    if (v0 + u * NT < b0) filter_vec_post<S, T, true>(ra[u], v0 + u * NT, c, POSTP, rthr, thr, buf, ctl);
             } else {
                 thr = t0;
 #pragma unroll
@@ -1796,7 +1822,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             int e = tid < n1 ? r1_lo + tid : r2_lo + (tid - n1);
             float raw = Elem<T>::load1(c.row, e);
             if (POST) {
-                if (raw >= rthr) consider_post<S, true>(buf, ctl, c, raw, e, thr);
+                if (raw >= rthr) consider_post<S, true>(buf, ctl, c, POSTP, raw, e, thr);
             } else {
                 float v = __fmul_rn(raw, c.inv_temp);
                 if (v >= thr) consider<S, true>(buf, ctl, c, raw, v, e, thr);
@@ -1830,7 +1856,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                 int e = e0 + j * NT + tid;
                 if (e < ehi) {
                     float l = Elem<T>::load1(c.row, e);
-                    if (POST) l = post_logit(l, c.post);
+                    if (POST) l = post_logit(l, POSTP);
                     if (c.pen_bitmap && bm_test(bm, e)) l = penalise(l, c.pen);
                     float v = __fmul_rn(l, c.inv_temp);
                     if (strict ? (v > thr) : (v >= thr)) append<S>(buf, ctl, v, e + c.voff);
@@ -1940,7 +1966,7 @@ __global__ void __launch_bounds__(WIDE_NT, 1) wide_rows_kernel(const KArgs a) {
     if (pen) build_penalty_bitmap(a, row, wp, hl, nullptr, V, a.vocab_offset, bm, tid, WIDE_NT);
 
     // scaled, penalised value of column e and its key
-    const Post post = {a.post_mode, a.post_scale, a.post_cap};
+    const Post& post = a.post;
     auto value = [&](int e) {
         float l = Elem<T>::load1(rowp, e);
         if (post.mode) l = post_logit(l, post);
@@ -2543,9 +2569,9 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
     a.part_cap = 0;
     a.parts = 0;
     a.hist_tma_ok = a.history && reinterpret_cast<uintptr_t>(a.history) % 16 == 0 && a.hist_stride % 4 == 0;
-    a.post_mode = post_mode_of(b->logit_scale, b->logit_softcap, b->flags);
-    a.post_scale = b->logit_scale;
-    a.post_cap = b->logit_softcap;
+    a.post.mode = post_mode_of(b->logit_scale, b->logit_softcap, b->flags);
+    a.post.scale = b->logit_scale;
+    a.post.cap = b->logit_softcap;
 #ifdef MANTLE_DEBUG_SWITCHES
     const char* dbg = getenv("MANTLE_SAMPLER_DEBUG");
     a.debug = dbg ? atoi(dbg) : 0;
@@ -2590,7 +2616,7 @@ int launch_scan_ldg_as(const KArgs& a, cudaStream_t stream) {
 
 template <class S, int MODE>
 int launch_scan_ldg(const KArgs& a, int dtype, cudaStream_t stream) {
-    if (a.post_mode)
+    if (a.post.mode)
         return dtype == MANTLE_DTYPE_F32 ? launch_scan_ldg_as<S, float, MODE, true>(a, stream)
                                          : launch_scan_ldg_as<S, bf16_t, MODE, true>(a, stream);
     return dtype == MANTLE_DTYPE_F32 ? launch_scan_ldg_as<S, float, MODE, false>(a, stream)
@@ -2599,7 +2625,7 @@ int launch_scan_ldg(const KArgs& a, int dtype, cudaStream_t stream) {
 
 template <int MODE>
 int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
-    if (use_ldg(a.max_top_k, a.post_mode != 0)) {
+    if (use_ldg(a.max_top_k, a.post.mode != 0)) {
         if (a.max_top_k <= ShapeLdg::KCAP) return launch_scan_ldg<ShapeLdg, MODE>(a, dtype, stream);
         return launch_scan_ldg<ShapeLdgLargeK, MODE>(a, dtype, stream);
     }
