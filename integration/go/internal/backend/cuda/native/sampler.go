@@ -40,12 +40,15 @@ typedef struct MantleSampleBatch {
 	int32_t* status;
 	int32_t cand_stride, splits;
 	uint32_t flags, reserved;
+	float logit_scale, logit_softcap;
 } MantleSampleBatch;
 
 extern int mantleCudaSampleRows(const MantleSampleBatch* b, void* ws, size_t wsBytes, cudaStream_t s);
 extern int mantleCudaSamplerWorkspaceBytes(const MantleSampleBatch* b, size_t* bytes);
 extern int mantleCudaSampleRowsNoAlloc(const MantleSampleBatch* b, cudaStream_t s);
 extern int mantleCudaArgMaxRowsF32(const float* x, int rows, int n, int64_t stride, int* out, cudaStream_t s);
+extern int mantleCudaLogitPostprocessRowsF32(float* x, int rows, int n, int64_t stride, float scale, float softcap,
+	uint32_t flags, cudaStream_t s);
 
 static int mantleCudaSampleRowsWrapper(const MantleSampleBatch* b, void* ws, size_t n, cudaStream_t s) {
 	return mantleCudaSampleRows(b, ws, n, s);
@@ -58,6 +61,10 @@ static int mantleCudaSampleRowsNoAllocWrapper(const MantleSampleBatch* b, cudaSt
 }
 static int mantleCudaArgMaxRowsF32Wrapper(const float* x, int rows, int n, int64_t stride, int* out, cudaStream_t s) {
 	return mantleCudaArgMaxRowsF32(x, rows, n, stride, out, s);
+}
+static int mantleCudaLogitPostprocessRowsF32Wrapper(float* x, int rows, int n, int64_t stride, float scale,
+	float softcap, uint32_t flags, cudaStream_t s) {
+	return mantleCudaLogitPostprocessRowsF32(x, rows, n, stride, scale, softcap, flags, s);
 }
 */
 import "C"
@@ -81,11 +88,20 @@ type SampleParams struct {
 	Uniform       float64
 }
 
+// HeadPost is what the model head does to the logits before sampling (LMHeadMultiplier and
+// FinalLogitSoftcap, simd/runtime.go:258-272).  The zero value means neither.
+type HeadPost struct {
+	Scale   float32 // applied when neither 0 nor 1
+	Softcap float32 // applied when > 0
+	Tanhf   bool    // tanhf as mantleCudaLogitSoftcapF32 has it, instead of the host path's fastTanh
+}
+
 // SampleRowsF32 samples `rows` rows of device-resident float32 logits.  params, history,
 // exclude and next are device buffers laid out as include/mantle_cuda_sampler.h describes;
-// workspace may be the zero DeviceBuffer when SamplerWorkspaceBytes reports 0.
+// workspace may be the zero DeviceBuffer when SamplerWorkspaceBytes reports 0.  post is
+// applied to the logits on the fly; they are not rewritten.
 func SampleRowsF32(logits DeviceBuffer, rows, vocab int, rowStride int64, params, history DeviceBuffer,
-	histStride int, exclude DeviceBuffer, nExclude int, maxTopK int, next, workspace DeviceBuffer,
+	histStride int, exclude DeviceBuffer, nExclude int, maxTopK int, post HeadPost, next, workspace DeviceBuffer,
 	workspaceBytes int64, stream Stream) error {
 	if logits.ptr == nil || params.ptr == nil || next.ptr == nil {
 		return fmt.Errorf("sample buffer is nil")
@@ -106,6 +122,11 @@ func SampleRowsF32(logits DeviceBuffer, rows, vocab int, rowStride int64, params
 	b.n_exclude = C.int32_t(nExclude)
 	b.params = (*C.MantleSampleParams)(params.ptr)
 	b.next = (*C.int32_t)(next.ptr)
+	b.logit_scale = C.float(post.Scale)
+	b.logit_softcap = C.float(post.Softcap)
+	if post.Tanhf {
+		b.flags |= 4 // MANTLE_SAMPLE_SOFTCAP_TANHF
+	}
 	return cudaErr(C.mantleCudaSampleRowsWrapper(&b, workspace.ptr, C.size_t(workspaceBytes), stream.ptr))
 }
 
@@ -119,6 +140,23 @@ func ArgMaxRowsF32To(x DeviceBuffer, rows, n int, stride int64, outIdx DeviceBuf
 	}
 	return cudaErr(C.mantleCudaArgMaxRowsF32Wrapper((*C.float)(x.ptr), C.int(rows), C.int(n), C.int64_t(stride),
 		(*C.int)(outIdx.ptr), stream.ptr))
+}
+
+// LogitPostprocessF32 rewrites device-resident logits in place: the multiplier loop and the soft
+// cap of the model head in one kernel.  It takes the place of LogitSoftcapF32 (softmax.go:62-77).
+func LogitPostprocessF32(data DeviceBuffer, rows, n int, stride int64, post HeadPost, stream Stream) error {
+	if data.ptr == nil {
+		return fmt.Errorf("logit postprocess buffer is nil")
+	}
+	if rows <= 0 || n <= 0 {
+		return fmt.Errorf("logit postprocess rows and n must be > 0")
+	}
+	var flags C.uint32_t
+	if post.Tanhf {
+		flags = 4
+	}
+	return cudaErr(C.mantleCudaLogitPostprocessRowsF32Wrapper((*C.float)(data.ptr), C.int(rows), C.int(n),
+		C.int64_t(stride), C.float(post.Scale), C.float(post.Softcap), flags, stream.ptr))
 }
 
 var _ = unsafe.Pointer(nil)
