@@ -355,7 +355,7 @@ def run_ours(args):
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": DRAM_TRAFFIC_RATIO * kernel_bytes if args.workload == "throughput" else None,
                 "peak_kind": "of %s" % peak_kind, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                "kernel": "wide_rows_kernel" if w.max_top_k > 1024 else ("scan_rows_ldg_kernel" if (w.max_top_k <= 256 or post) else "scan_rows_kernel"), "algorithmic_bytes_per_launch": kernel_bytes,
+                "kernel": "wide_rows_kernel" if w.max_top_k > 1024 else "scan_rows_ldg_kernel", "algorithmic_bytes_per_launch": kernel_bytes,
                 "bytes_per_row": w.bytes_per_row,
             },
             "cpu_baseline": cpu,
