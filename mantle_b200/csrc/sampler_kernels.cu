@@ -270,14 +270,12 @@ __device__ __forceinline__ float post_raw_bound(float thr, float inv_temp, const
     if (p.mode & POST_SCALE) q = q / p.scale;
     return q - fabsf(q) * 1e-4f;
 }
-// A value that at least as many columns reach as have a raw logit >= raw0 (the seed of the threshold).
-__device__ __forceinline__ float post_seed_value(float raw0, float inv_temp, const Post& p) {
-    const float ninf = __uint_as_float(0xff800000u);
-    if (!(raw0 > ninf)) return ninf;
-    const float v0 = __fmul_rn(post_logit(raw0, p), inv_temp);
-    if (!(fabsf(v0) < 3.0e38f)) return v0;  // an infinite value is its own bound
-    const float slack = (p.mode & POST_CAP) ? 4.0f * POST_EPS * p.cap * inv_temp : 0.0f;
-    return v0 - slack - fabsf(v0) * 1e-5f;
+// A post-processed logit that every column with a raw logit >= raw0 reaches (the seed of the threshold).
+__device__ __forceinline__ float post_seed_logit(float raw0, const Post& p) {
+    const float l0 = post_logit(raw0, p);
+    if (!(fabsf(l0) < 3.0e38f)) return l0;  // an infinite value is its own bound
+    const float slack = (p.mode & POST_CAP) ? 4.0f * POST_EPS * p.cap : 0.0f;
+    return l0 - slack - fabsf(l0) * 1e-5f;
 }
 
 template <typename T>
@@ -460,20 +458,6 @@ __device__ __forceinline__ float vec_max_raw(const uint4& rawv) {
     float m = raw[0];
 #pragma unroll
     for (int j = 1; j < VEC; j++) m = fmaxf(m, raw[j]);
-    return m;
-}
-
-// The largest raw logit among the columns of one complete vector that carry no penalty.
-template <typename T>
-__device__ __forceinline__ float vec_max_raw_unpenalised(const uint4& rawv, int vec, const RowCtx& c) {
-    constexpr int VEC = Elem<T>::VEC;
-    float raw[VEC];
-    Elem<T>::widen(rawv, raw);
-    const int e0 = vec * VEC - c.mis;
-    float m = __uint_as_float(0xff800000u);
-#pragma unroll
-    for (int j = 0; j < VEC; j++)
-        if (!(c.pen_bitmap && bm_test(c.bm, e0 + j))) m = fmaxf(m, raw[j]);
     return m;
 }
 
@@ -841,7 +825,8 @@ __device__ void sample_tail(const KArgs& a, int row, const MantleSampleParams& P
     }
 }
 
-__host__ __device__ inline size_t bitmap_words(int vocab) { return (size_t)((vocab + 31) / 32 + 2); }
+// words of the penalty bitmap: V bits, padded to whole 16-byte vectors
+__host__ __device__ inline size_t bitmap_words(int vocab) { return (size_t)(((vocab + 31) / 32 + 2 + 3) & ~3); }
 
 // The same tail for shortlists of at most 64 entries, run by one warp with the shortlist in
 // registers (lane L holds entries L and L+32): no CTA barrier, no shared-memory round trips.
@@ -1136,6 +1121,45 @@ __device__ void build_penalty_bitmap(const KArgs& a, int row, const WinPlan& w, 
         }
     }
     __syncthreads();
+}
+
+// The same bitmap for the plain-load kernel, arranged for latency: the window's ids are requested
+// first and travel while the bitmap is zeroed (with 16-byte stores); the barrier after the clears
+// is the caller's.  (Measured: the bitmap phase cost a tenth of the kernel's time before.)
+template <int NT>
+__device__ __forceinline__ void build_penalty_bitmap_early(const KArgs& a, int row, const WinPlan& w, int hl, int V,
+                                                           int voff, uint32_t* bm, int tid) {
+    constexpr int PRE = 4;  // ids per thread fetched ahead: windows of up to PRE * NT ids
+    const int32_t* h = a.history + (size_t)row * (size_t)a.hist_stride;
+    int ids[PRE];
+#pragma unroll
+    for (int u = 0; u < PRE; u++) {
+        const int j = w.start + u * NT + tid;
+        ids[u] = j < hl ? __ldg(h + j) : -1;
+    }
+    uint4* bm4 = reinterpret_cast<uint4*>(bm);
+    const int nvec = (int)(bitmap_words(V) / 4);
+    for (int i = tid; i < nvec; i += NT) bm4[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    auto mark = [&](int id) {
+        if (id >= 0 && id < a.vocab_total) {  // sampler.go:116
+            id -= voff;
+            if (id >= 0 && id < V) atomicOr(&bm[id >> 5], 1u << (id & 31));
+        }
+    };
+#pragma unroll
+    for (int u = 0; u < PRE; u++) mark(ids[u]);
+    for (int j = w.start + PRE * NT + tid; j < hl; j += NT) mark(h[j]);
+    if (a.n_exclude > 0) {  // sampler.go:122-126, after every set
+        __syncthreads();
+        for (int j = tid; j < a.n_exclude; j += NT) {
+            int id = a.exclude[j];
+            if (id >= 0 && id < a.vocab_total) {
+                id -= voff;
+                if (id >= 0 && id < V) atomicAnd(&bm[id >> 5], ~(1u << (id & 31)));
+            }
+        }
+    }
 }
 
 __device__ __forceinline__ int history_len(const KArgs& a, int row) {
@@ -1671,12 +1695,10 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     // loads are issued, so that those loads find their lines on the way or already there
     auto ahead = [&](int r) {
 #if LDG_PREFETCH
-        if (r < nreg && (tid & 7) == 0) {
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                int v = a0 + r * RV + u * NT + tid;
-                if (v < b0) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(vbase + v));
-            }
+        // a warp's share of a region is U runs of 512 bytes: lane i asks for line i & 3 of run i >> 2
+        if (r < nreg && lane < 4 * U) {
+            const int v = a0 + r * RV + (lane >> 2) * NT + (tid & ~31) + (lane & 3) * 8;
+            if (v < b0) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(vbase + v));
         }
 #endif
     };
@@ -1692,7 +1714,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     WinPlan wp = win_plan(a, P, hl);
     wp.staged = false;
     if (wp.active) {
-        build_penalty_bitmap(a, row, wp, hl, nullptr, c.V, c.voff, bm, tid, NT);
+        build_penalty_bitmap_early<NT>(a, row, wp, hl, c.V, c.voff, bm, tid);
         c.pen_bitmap = true;
     }
     __syncthreads();
@@ -1751,12 +1773,14 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         if (nreg > 1) load(rb, 1);
         {
             const int v0 = a0 + tid;
+            // Thread maxima of the RAW logits: everything between a raw logit and its final value
+            // (post-processing up to its slack, penalty, temperature) is non-decreasing, and a
+            // column's value is at least what it would be with the penalty, so the image of a raw
+            // logit that k columns reach is a value that k columns reach -- no bitmap lookups here.
             float tmax = __uint_as_float(0xff800000u);
 #pragma unroll
             for (int u = 0; u < U; u++)
-                if (v0 + u * NT < b0)
-                    tmax = fmaxf(tmax, POST ? vec_max_raw_unpenalised<T>(ra[u], v0 + u * NT, c)
-                                            : vec_max_penalised<T>(ra[u], v0 + u * NT, c));
+                if (v0 + u * NT < b0) tmax = fmaxf(tmax, vec_max_raw<T>(ra[u]));
             float x = tmax;  // bitonic sort across the warp, descending
 #pragma unroll
             for (int k2 = 2; k2 <= 32; k2 <<= 1) {
@@ -1775,9 +1799,11 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             float t0 = ctl->warpv[0];
 #pragma unroll
             for (int w = 1; w < NWARP; w++) t0 = fminf(t0, ctl->warpv[w]);
+            if (POST) t0 = post_seed_logit(t0, POSTP);
+            if (c.pen_bitmap) t0 = penalise(t0, c.pen);
+            t0 = __fmul_rn(t0, c.inv_temp);
             if (POST) {
-                // t0 is a raw logit that k unpenalised columns of this region reach
-                thr = post_seed_value(t0, c.inv_temp, POSTP);
+                thr = t0;
                 rthr = post_raw_bound(thr, c.inv_temp, POSTP);
 #pragma unroll
                 for (int u = 0; u < U; u++)
