@@ -160,6 +160,20 @@ int mantleCudaLogitPostprocessRowsF32(float* logits, int rows, int vocab, int64_
                                       mantleCudaStream_t stream);
 
 /*
+ * The decode loop's `toks = append(toks, next)` (internal/inference/engine.go:244-250) for a
+ * batch whose histories stay on the device between steps, so that a step uploads no history:
+ * history[r][hist_len[r]++] = next[r] for every row.  A row whose token is one of the `stop`
+ * ids (the reference leaves its loop before appending a stop token) or negative is not
+ * appended; it is marked in done[r] when `done` is given, and rows already marked are left
+ * alone.  When a row's buffer is full its `keep` most recent ids move to the front first;
+ * keep <= hist_stride / 2, and the penalty window stays exact while keep is at least the
+ * largest repeat_last_n in use.  Queue it behind mantleCudaSampleRows on the same stream.
+ */
+int mantleCudaHistoryAppendRows(int32_t* history, int32_t* hist_len, int hist_stride, int rows,
+                                const int32_t* next, int keep, const int32_t* stop, int n_stop,
+                                int32_t* done, mantleCudaStream_t stream);
+
+/*
  * Index of the maximum of each row, the lowest index on ties (argmax,
  * sampler.go:237-250).  Batched replacement for mantleCudaArgMaxF32
  * (native/softmax.cu:663-704,1151-1160), whose tie-break follows thread order.

@@ -1208,6 +1208,41 @@ __global__ void __launch_bounds__(PENALTY_NT) penalty_rows_kernel(const KArgs a)
 // the stage just freed.  Thread 0 also looks one item ahead: the next item's parameters,
 // history length and history window are in shared memory before the item starts.
 
+// The decode loop's `toks = append(toks, next)` (inference/engine.go:244-250) for a batch whose
+// histories live on the device: one warp per row.  A row whose token is a stop token (or
+// negative: the sampler reported an error) is marked done and left alone, as the reference
+// leaves the loop before it appends; rows already done stay untouched.  A full buffer first
+// moves its `keep` most recent ids to the front (keep <= hist_stride / 2, so the two ranges
+// never overlap): the penalty window, the last repeat_last_n ids, is unchanged while keep
+// covers it.
+__global__ void __launch_bounds__(256) history_append_rows_kernel(int32_t* history, int32_t* hist_len, int hist_stride,
+                                                                  int rows, const int32_t* next, int keep,
+                                                                  const int32_t* stop, int n_stop, int32_t* done) {
+    const int row = (int)((blockIdx.x * (unsigned)blockDim.x + threadIdx.x) >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    if (done && done[row] != 0) return;
+    const int tok = next[row];
+    bool is_stop = tok < 0;
+    for (int j = lane; j < n_stop; j += 32) is_stop |= stop[j] == tok;
+    is_stop = __any_sync(0xffffffffu, is_stop);
+    if (is_stop) {
+        if (done && lane == 0) done[row] = 1;
+        return;
+    }
+    int32_t* h = history + (size_t)row * (size_t)hist_stride;
+    int len = min(max(hist_len[row], 0), hist_stride);
+    if (len == hist_stride) {
+        for (int j = lane; j < keep; j += 32) h[j] = h[len - keep + j];
+        len = keep;
+        __syncwarp();
+    }
+    if (lane == 0) {
+        h[len] = tok;
+        hist_len[row] = len + 1;
+    }
+}
+
 // The post-processing alone, in place: what the reference does to the whole logits vector before
 // it samples (simd/runtime.go:258-272; device form native/softmax.cu:963-970).  For callers that
 // want the rewritten logits; the sampler itself applies it on the fly and writes nothing.
@@ -2768,6 +2803,18 @@ extern "C" int mantleCudaLogitPostprocessRowsF32(float* logits, int rows, int vo
     const long long n = (long long)rows * vocab;
     const int grid = (int)std::min<long long>((n + 255) / 256, (long long)smem_budget().sms * 32);
     postprocess_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_)>>>(logits, rows, vocab, row_stride, post);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int mantleCudaHistoryAppendRows(int32_t* history, int32_t* hist_len, int hist_stride, int rows,
+                                          const int32_t* next, int keep, const int32_t* stop, int n_stop,
+                                          int32_t* done, mantleCudaStream_t stream_) {
+    if (!history || !hist_len || !next || rows <= 0 || hist_stride < 2) return kInvalid;
+    if (keep < 0 || keep > hist_stride / 2 || n_stop < 0 || (n_stop > 0 && !stop)) return kInvalid;
+    const long long threads = (long long)rows * 32;
+    if ((threads + 255) / 256 > 0x7fffffffLL) return kInvalid;
+    history_append_rows_kernel<<<(int)((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+        history, hist_len, hist_stride, rows, next, keep, stop, n_stop, done);
     return (int)cudaGetLastError();
 }
 

@@ -81,6 +81,10 @@ EXPORTS = {
         C.c_int,
         [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_float, C.c_float, C.c_uint32, C.c_void_p],
     ),
+    "mantleCudaHistoryAppendRows": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p],
+    ),
     "mantleCudaArgMaxRowsF32": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_void_p]),
     "mantleCudaSampleLocalTopK": (
         C.c_int,

@@ -176,6 +176,17 @@ def logit_postprocess_rows_(logits, logit_scale=0.0, logit_softcap=0.0, flags=0,
     return logits
 
 
+def history_append_rows_(history, hist_len, next_tokens, keep, stop=None, done=None, stream=None):
+    """`toks = append(toks, next)` of the reference's decode loop (inference/engine.go:244-250) for
+    device-resident histories: [rows, stride] int32 ids, [rows] int32 lengths, both updated in place."""
+    lib = native.load()
+    with torch.cuda.device(history.device):
+        rc = lib.mantleCudaHistoryAppendRows(history.data_ptr(), hist_len.data_ptr(), history.shape[1],
+                                             history.shape[0], next_tokens.data_ptr(), keep, _ptr(stop),
+                                             0 if stop is None else stop.numel(), _ptr(done), _stream_ptr(stream))
+    native.check(rc, "mantleCudaHistoryAppendRows")
+
+
 def repeat_penalty_rows_(logits, params, history, hist_len=None, exclude=None, stream=None):
     """The reference's in-place repeat penalty alone (sampler.go:99-138) on float32 rows."""
     lib = native.load()

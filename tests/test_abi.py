@@ -93,6 +93,10 @@ def test_invalid_arguments_are_rejected_on_the_host():
     assert lib.mantleCudaSampleLocalTopK(C.byref(good_batch()), 500, 1000, 0x10, 0x10, 0x10, 40, None) == inv
     assert lib.mantleCudaSampleMergeParts(C.byref(good_batch()), 200, 0x10, 0x10, 0x10, 40, None) == inv
     assert lib.mantleCudaRepeatPenaltyRowsF32(None, None) == inv
+    assert lib.mantleCudaHistoryAppendRows(None, 0x10, 64, 4, 0x10, 32, None, 0, None, None) == inv
+    assert lib.mantleCudaHistoryAppendRows(0x10, 0x10, 64, 4, 0x10, 33, None, 0, None, None) == inv  # keep > stride/2
+    assert lib.mantleCudaHistoryAppendRows(0x10, 0x10, 64, 0, 0x10, 32, None, 0, None, None) == inv
+    assert lib.mantleCudaHistoryAppendRows(0x10, 0x10, 64, 4, 0x10, 32, None, 2, None, None) == inv  # stop list missing
 
 
 def test_constructor_normalisation_matches_the_oracle():
