@@ -437,3 +437,21 @@ def test_bounded_wait_gives_up_and_reports():
     # the context is still good: sample something
     g, _ = one([-1, 5, 3, 7, 2], temperature=0.0)
     assert g["next"][0] == 3
+
+
+def test_committed_fixtures():
+    """The CUDA path against tests/golden/oracle_cases.npz: inputs and oracle answers committed
+    together, without and with the model head's multiplier and soft cap."""
+    import os
+
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_cases.npz"))
+    params = z["params"].view(O.PARAMS_DTYPE)
+    cap = z["cand_idx"].shape[1]
+    for prefix, kw in (("", {}), ("post_", dict(logit_scale=float(z["post_scale"]), logit_softcap=float(z["post_cap"])))):
+        d = torch.from_numpy(z["logits"].copy()).to(DEV)
+        g = run_gpu(d, params, 300, history=z["history"], hist_len=z["hist_len"], exclude=z["exclude"], cand_cap=cap,
+                    **kw)
+        ref = dict(next=z[prefix + "next"], n_kept=z[prefix + "n_kept"], cut=z[prefix + "cut"],
+                   cand_idx=z[prefix + "cand_idx"], cand_prob=z[prefix + "cand_prob"])
+        compare(g, ref, cap, where="fixture " + (prefix or "plain"))
+        assert g["status"] == 0

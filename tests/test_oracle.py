@@ -260,3 +260,66 @@ def test_fast_tanh_error_bound():
     xs = np.concatenate([rng.uniform(-10, 10, 200000), rng.uniform(-0.5, 0.5, 100000)]).astype(np.float32)
     got = O.postprocess(xs.copy(), 0.0, 1.0)
     assert np.max(np.abs(got.astype(np.float64) - np.tanh(xs.astype(np.float64)))) < 3e-6
+
+
+# ---- committed fixtures (tests/golden) ------------------------------------------------------------
+
+def load_golden():
+    import json
+    import os
+
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    with open(os.path.join(here, "reference_vectors.json")) as f:
+        ref = json.load(f)["cases"]
+    z = np.load(os.path.join(here, "oracle_cases.npz"))
+    return ref, z
+
+
+def test_reference_vectors_file():
+    """Every expected value the reference's tests hold, from the committed transcription."""
+    ref, _ = load_golden()
+    assert len(ref) == 5
+    for case in ref:
+        toks = []
+        for u in case["uniforms"]:
+            out, _ = run1(case["logits"], uniform=u, **case["config"])
+            toks.append(int(out["next"][0]))
+            if "expect_next" in case:
+                assert toks[-1] == case["expect_next"], case["source"]
+            if "expect_cut" in case:
+                assert int(out["cut"][0]) == case["expect_cut"], case["source"]
+            if "expect_n_kept" in case:
+                assert int(out["n_kept"][0]) == case["expect_n_kept"], case["source"]
+        if case.get("expect_same_token_for_equal_uniforms"):
+            assert len(set(toks)) == 1, case["source"]
+
+
+def test_oracle_reproduces_the_committed_cases():
+    """The oracle has not drifted from the answers committed with its inputs, with and without the
+    model head's post-processing; make_fixtures.py wrote them."""
+    _, z = load_golden()
+    params = z["params"].view(O.PARAMS_DTYPE)
+    for prefix, scale, cap in (("", 0.0, 0.0), ("post_", float(z["post_scale"]), float(z["post_cap"]))):
+        lg = z["logits"].copy()
+        if prefix:
+            O.postprocess(lg, scale, cap)
+        out = O.sample_rows(lg, params, history=z["history"], hist_len=z["hist_len"], exclude=z["exclude"],
+                            cand_cap=z["cand_idx"].shape[1])
+        assert np.array_equal(out["next"], z[prefix + "next"])
+        assert np.array_equal(out["n_kept"], z[prefix + "n_kept"])
+        assert np.array_equal(out["cut"], z[prefix + "cut"])
+        assert np.array_equal(out["cand_idx"], z[prefix + "cand_idx"])
+        assert np.array_equal(out["cand_prob"], z[prefix + "cand_prob"])
+    assert len(set(z["next"].tolist())) > 10  # the batch is not degenerate
+
+
+def test_second_restatement_reproduces_the_committed_cases():
+    """The numpy restatement (written independently of the C oracle) gives the committed tokens."""
+    _, z = load_golden()
+    params = z["params"].view(O.PARAMS_DTYPE)
+    for r in range(0, z["logits"].shape[0], 3):
+        hl = int(z["hist_len"][r])
+        tok, idx, prob, cut = pyref.sample(z["logits"][r].copy(), z["history"][r, :hl].tolist(),
+                                           z["exclude"].tolist(), params[r])
+        assert tok == int(z["next"][r]), r
+        assert cut == int(z["cut"][r]), r
