@@ -1,0 +1,47 @@
+// merge_parts_kernel: merges the local shortlists of a split row or of vocabulary shards.
+// Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
+// translation unit.
+#pragma once
+
+namespace {
+
+// Merge of `parts` local shortlists per row (several CTAs of one GPU, or one per
+// vocabulary shard after an all-gather), then the tail.
+__global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_parts_kernel(const KArgs a) {
+    using S = ShapeLargeK;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
+    Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
+    const int tid = threadIdx.x;
+    const int row = blockIdx.x;
+
+    const MantleSampleParams P = row_params(a, row);
+    const bool greedy = P.greedy != 0 || (P.top_k == 1 && P.top_p >= 1.0f && P.temperature == 1.0f);
+    int k = greedy ? 1 : min(P.top_k, a.vocab_total);
+    const bool bad_k = !greedy && (k > a.max_top_k || k > KMAX || k < 1);
+
+    if (tid == 0) ctl->cnt = 0;
+    __syncthreads();
+    for (int p = 0; p < a.parts; p++) {
+        const size_t slot = (size_t)p * a.rows + row;
+        const int m = min(a.part_cnt[slot], a.part_cap);
+        for (int i = tid; i < m; i += S::NT)
+            append<S>(buf, ctl, a.part_val[slot * a.part_cap + i], a.part_idx[slot * a.part_cap + i]);
+    }
+    if (bad_k) {
+        if (tid == 0) {
+            if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_TOPK_RANGE);
+            a.next[row] = -1;
+            if (a.n_kept) a.n_kept[row] = 0;
+            if (a.cut) a.cut[row] = 0;
+        }
+        return;
+    }
+    bool have, ordered;
+    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
+    __syncthreads();
+    finish_row<S, MODE_FUSED>(a, row, 0, P, greedy, ordered, buf, ctl, tid);
+}
+
+}  // namespace

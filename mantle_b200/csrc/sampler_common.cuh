@@ -1,0 +1,448 @@
+// Shapes, shared-memory records, kernel arguments and the per-column helpers (keys, fastExp,
+// penalty, head post-processing, the filter and the candidate buffer) every sampler kernel shares.
+// Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
+// translation unit.
+#pragma once
+
+namespace {
+
+constexpr int KMAX = MANTLE_SAMPLE_MAX_TOP_K;
+constexpr int RANK_MAX = 256;  // largest buffer the counting select takes
+constexpr int HIST_CAP = 1024; // history-window ids staged in shared memory ahead of their row
+constexpr int MAX_STAGES = 8;
+
+// Launch shape of one kernel instantiation.
+//   NT    threads per CTA            U     16-byte vectors per thread per chunk
+//   CAP   candidate buffer entries   KCAP  largest top_k this shape serves
+//   MINB  CTAs per SM the register budget is held to
+template <int NT_, int U_, int CAP_, int KCAP_, int MINB_>
+struct Shape {
+    static constexpr int NT = NT_, U = U_, CAP = CAP_, KCAP = KCAP_, MINB = MINB_;
+    static constexpr int NWARP = NT / 32;
+    static constexpr int EPT = (CAP + NT - 1) / NT;  // candidate entries per thread during compaction
+    // columns per thread per step of the careful path: a whole step always fits the buffer
+    static constexpr int SLOW_EPT = (CAP - KCAP) / NT < 4 ? (CAP - KCAP) / NT : 4;
+    static_assert(SLOW_EPT >= 1, "careful path needs room");
+    static_assert(KCAP + NT * SLOW_EPT <= CAP, "careful path needs room for one full step");
+    static_assert(KCAP * 24 <= CAP * 8, "ordered shortlist must fit behind the survivors");
+    static_assert(RANK_MAX <= NT, "counting select: one entry per thread");
+    // shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [Pre] [window ids[HIST_CAP]] [ring] [bitmap]
+    static constexpr size_t SMEM_FIXED = 8 * (size_t)CAP + 4 * 256 + 512 + 256 + 4 * (size_t)HIST_CAP;
+};
+// Measured on B200 (a bare copy loop over 2.5 GB): the time one bulk copy takes to land hardly
+// depends on its size (about 0.6 us for 8, 16 and 32 KB alike) and deeper rings do not raise a
+// CTA's copy rate, so bandwidth comes from chunk size times CTAs per SM.  With the sampler's
+// serial phases per row (bitmap, cuts, tail) three CTAs of 256 threads with 16 KB chunks
+// overlap better than two with 32 KB chunks (71 % against 69 % of measured HBM bandwidth).
+using ShapeSmallK = Shape<256, 4, 2048, 256, 3>;   // top_k <= 256: 16 KB candidate buffer
+using ShapeLargeK = Shape<512, 4, 4096, KMAX, 1>;  // top_k <= 1024: 32 KB candidate buffer
+#ifndef LDG_VOTE_EVERY
+#define LDG_VOTE_EVERY 2
+#endif
+#ifndef LDG_PREFETCH
+#define LDG_PREFETCH 1
+#endif
+#ifndef LDG_NT
+#define LDG_NT 256
+#define LDG_U 4
+#define LDG_MINB 4
+#endif
+using ShapeLdg = Shape<LDG_NT, LDG_U, 2048, 256, LDG_MINB>;  // the plain-load kernel: four CTAs per SM
+using ShapeLdgLargeK = Shape<512, 4, 4096, KMAX, 1>;         // the plain-load kernel for top_k <= 1024
+using ShapeAlt = Shape<256, 8, 2048, 256, 2>;      // tuning: MANTLE_SAMPLER_SHAPE=alt (32 KB chunks)
+constexpr int MAX_NWARP = 32;
+constexpr int MERGE_CAP = ShapeLargeK::CAP;
+
+constexpr int POST_SCALE = 1, POST_CAP = 2, POST_TANHF = 4;
+
+constexpr int MODE_FUSED = 0;    // one CTA per row, tail in the same kernel
+constexpr int MODE_PARTS = 1;    // several CTAs per row (or one vocabulary shard): write the local shortlist
+
+struct Cand {
+    uint32_t key;  // order-preserving image of the scaled value
+    uint32_t idx;  // token id (global)
+};
+
+// Per-CTA control block in shared memory.
+struct Ctl {
+    int cnt;            // live entries in the candidate buffer
+    int sel_bin;        // radix select: chosen digit
+    int sel_need;       //               entries still wanted inside the chosen digit
+    int sel_cnt;        //               entries inside the chosen digit
+    uint32_t kmin, kmax;
+    int n_after;        // shortlist length after min-p
+    int cut;
+    int pos;
+    int pad;
+    double sum;
+    double new_sum;
+    float warpv[MAX_NWARP];
+    uint32_t warpk_min[MAX_NWARP];
+    uint32_t warpk_max[MAX_NWARP];
+    uint64_t full[MAX_STAGES];  // one mbarrier per ring stage: "the chunk has landed"
+    int abort;                  // a wait on a copy ran out
+};
+static_assert(sizeof(Ctl) <= 512 && sizeof(Ctl) % 8 == 0, "control block outgrew its slot");
+
+// What thread 0 fetches ahead for the item after the current one -- its parameters and history
+// length (small asynchronous copies) and, tracked by `win_full`, its history window -- and the
+// producer's own state, kept here rather than in registers that every thread would set aside.
+struct Pre {
+    MantleSampleParams p[2];
+    int hl[2];
+    int pad[2];
+    uint64_t win_full;
+    uint64_t pol;          // L2 eviction policy of the bulk copies
+    const uint4* p_vbase;  // item being issued: its row rounded down to 16 bytes,
+    int p_item, p_chunk, p_nchunks, p_a0, p_b0;  // its id, next chunk, chunk count, vector range
+    uint32_t g_issued;     // chunks issued so far
+    uint32_t w_issued;     // staged windows requested so far
+};
+static_assert(sizeof(Pre) <= 256, "prefetch block outgrew its slot");
+
+// Post-processing of the model head's output, applied to every logit before the sampler sees
+// it: POST_SCALE l *= scale; POST_CAP l = tanh(l / cap) * cap (POST_TANHF picks tanhf).
+struct Post {
+    int mode;
+    float scale, cap;
+};
+
+struct KArgs {
+    const void* logits;
+    int64_t row_stride;
+    int rows;
+    int vocab;         // columns held here
+    int vocab_offset;  // global id of column 0
+    int vocab_total;   // width of the whole row (for k = min(top_k, V))
+    const int32_t* history;
+    const int32_t* hist_len;
+    int hist_stride;
+    int n_exclude;
+    const int32_t* exclude;
+    const MantleSampleParams* params;  // NULL: every row is a plain argmax
+    int splits;
+    int max_top_k;
+    uint32_t flags;
+    int32_t* next;
+    int32_t* cand_idx;
+    double* cand_prob;
+    int32_t* n_kept;
+    int32_t* cut;
+    int32_t* status;
+    int cand_stride;
+    // MODE_PARTS outputs / merge inputs: part p of row r at (p*rows + r)*part_cap
+    float* part_val;
+    int32_t* part_idx;
+    int32_t* part_cnt;
+    int part_cap;
+    int parts;
+    int hist_tma_ok;  // history base 16-byte aligned and hist_stride a multiple of 4
+    Post post;  // read from the kernel's parameter space where it is used, never copied to registers
+#ifdef MANTLE_DEBUG_SWITCHES
+    int debug;
+#endif
+};
+
+// ---------------------------------------------------------------------------------------
+// small helpers
+
+// Barrier among the N threads of a CTA launched with exactly N threads.
+template <int N>
+__device__ __forceinline__ void csync() {
+    __syncthreads();
+}
+
+__device__ __forceinline__ uint32_t f2key(float v) {
+    v = __fadd_rn(v, 0.0f);  // -0.0 -> +0.0: the reference compares floats, for which they are equal
+    uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ float key2f(uint32_t k) {
+    uint32_t b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(b);
+}
+
+// fastExp, sampler.go:10-31, operation for operation in float32.
+__device__ __forceinline__ float fast_exp(float x) {
+    if (x > 88.0f) return 3.4028235e38f;
+    if (x < -88.0f) return 0.0f;
+    const float ln2 = 0.693147180559945309417f;
+    const float ln2inv = 1.44269504088896340736f;
+    float t = __fmul_rn(x, ln2inv);
+    int k = (x < 0.0f) ? __float2int_rz(__fsub_rn(t, 0.5f)) : __float2int_rz(__fadd_rn(t, 0.5f));
+    float r = __fsub_rn(x, __fmul_rn((float)k, ln2));
+    float r2 = __fmul_rn(r, r);
+    float r3 = __fmul_rn(r2, r);
+    float r4 = __fmul_rn(r2, r2);
+    float poly = __fadd_rn(1.0f, r);
+    poly = __fadd_rn(poly, __fmul_rn(r2, 0.5f));
+    poly = __fadd_rn(poly, __fmul_rn(r3, 0.16666667f));
+    poly = __fadd_rn(poly, __fmul_rn(r4, 0.041666667f));
+    poly = __fadd_rn(poly, __fmul_rn(__fmul_rn(r4, r), 0.008333333f));
+    float scale = __uint_as_float((uint32_t)(k + 127) << 23);
+    return __fmul_rn(poly, scale);
+}
+
+// sampler.go:132-136
+__device__ __forceinline__ float penalise(float l, float p) {
+    return l > 0.0f ? __fdiv_rn(l, p) : __fmul_rn(l, p);
+}
+
+// fastTanh, simd/ops.go:165-175, operation for operation in float32.
+__device__ __forceinline__ float fast_tanh(float x) {
+    if (x > 10.0f) return 1.0f;
+    if (x < -10.0f) return -1.0f;
+    const float e2x = fast_exp(__fmul_rn(2.0f, x));
+    return __fdiv_rn(__fsub_rn(e2x, 1.0f), __fadd_rn(e2x, 1.0f));
+}
+
+// What the model head does to a logit before the sampler sees it (simd/runtime.go:258-272):
+// the multiplier first, then the soft cap, with the host path's fastTanh or, on request, with
+// tanhf as the reference's device kernel has it (native/softmax.cu:963-970).
+__device__ __forceinline__ float post_logit(float l, const Post& p) {
+    if (p.mode & POST_SCALE) l = __fmul_rn(l, p.scale);
+    if (p.mode & POST_CAP) {
+        const float b = __fdiv_rn(l, p.cap);
+        const float t = (p.mode & POST_TANHF) ? tanhf(b) : fast_tanh(b);
+        l = __fmul_rn(t, p.cap);
+    }
+    return l;
+}
+
+// The streaming kernels never evaluate post_logit on a column that cannot matter.  The true map
+// g(l) = inv_temp * cap * tanh(l * scale / cap) is increasing, and what the device computes
+// differs from it by less than POST_EPS * cap * inv_temp (fastTanh: 1.7e-6 absolute, the
+// worst over every float32 in [-10, 10]; tanhf: 3e-7; the roundings of the multiplies and
+// divides: 3e-7 relative), so a threshold on the computed values turns into a threshold on the raw
+// logits: every column whose computed value reaches `thr` has a raw logit of at least
+// post_raw_bound(thr).  The margins are several times the error they cover; a wider margin only
+// lets a few more columns through to the exact test.
+constexpr float POST_EPS = 1e-5f;
+__device__ __forceinline__ float post_raw_bound(float thr, float inv_temp, const Post& p) {
+    const float ninf = __uint_as_float(0xff800000u);
+    if (!(thr > ninf)) return ninf;
+    float q = thr / inv_temp;
+    if (!(fabsf(q) > 1e-30f) || !(fabsf(q) < 1e30f)) return ninf;  // at zero the roundings are not relative
+    if (p.mode & POST_CAP) {
+        float y = q / p.cap - 10.0f * POST_EPS;
+        if (y <= -1.0f) return ninf;
+        y = fminf(y, 1.0f - 1e-6f);
+        q = 0.5f * logf((1.0f + y) / (1.0f - y)) * p.cap;  // atanh
+        if (!(fabsf(q) > 1e-30f)) return ninf;
+    }
+    if (p.mode & POST_SCALE) q = q / p.scale;
+    return q - fabsf(q) * 1e-4f;
+}
+// A post-processed logit that every column with a raw logit >= raw0 reaches (the seed of the threshold).
+__device__ __forceinline__ float post_seed_logit(float raw0, const Post& p) {
+    const float l0 = post_logit(raw0, p);
+    if (!(fabsf(l0) < 3.0e38f)) return l0;  // an infinite value is its own bound
+    const float slack = (p.mode & POST_CAP) ? 4.0f * POST_EPS * p.cap : 0.0f;
+    return l0 - slack - fabsf(l0) * 1e-5f;
+}
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+    static constexpr int VEC = 4;
+    __device__ static __forceinline__ void widen(const uint4& r, float* o) {
+        o[0] = __uint_as_float(r.x);
+        o[1] = __uint_as_float(r.y);
+        o[2] = __uint_as_float(r.z);
+        o[3] = __uint_as_float(r.w);
+    }
+    __device__ static __forceinline__ float load1(const void* p, int64_t e) {
+        return __ldcs(reinterpret_cast<const float*>(p) + e);
+    }
+};
+struct bf16_t {
+    uint16_t bits;
+};
+template <>
+struct Elem<bf16_t> {
+    static constexpr int VEC = 8;
+    __device__ static __forceinline__ void widen(const uint4& r, float* o) {
+        o[0] = __uint_as_float(r.x << 16);
+        o[1] = __uint_as_float(r.x & 0xffff0000u);
+        o[2] = __uint_as_float(r.y << 16);
+        o[3] = __uint_as_float(r.y & 0xffff0000u);
+        o[4] = __uint_as_float(r.z << 16);
+        o[5] = __uint_as_float(r.z & 0xffff0000u);
+        o[6] = __uint_as_float(r.w << 16);
+        o[7] = __uint_as_float(r.w & 0xffff0000u);
+    }
+    __device__ static __forceinline__ float load1(const void* p, int64_t e) {
+        uint16_t h = __ldcs(reinterpret_cast<const uint16_t*>(p) + e);
+        return __uint_as_float((uint32_t)h << 16);
+    }
+};
+
+// What a CTA knows about its row while it streams.
+struct RowCtx {
+    const void* row;      // row pointer
+    int mis;              // elements between the 16-byte boundary below the row pointer and the pointer
+    int V;                // columns
+    int voff;             // global id of column 0
+    float inv_temp;
+    float pen;
+    bool pen_bitmap;      // the penalty is applied from the bitmap (logits stay read-only)
+    const uint32_t* bm;   // bitmap, bit e set: column e is penalised
+};
+
+__device__ __forceinline__ bool bm_test(const uint32_t* bm, int e) { return (bm[e >> 5] >> (e & 31)) & 1u; }
+
+__device__ __forceinline__ int live_count(const Ctl* ctl) {
+    return *reinterpret_cast<const volatile int*>(&ctl->cnt);
+}
+
+template <class S>
+__device__ __forceinline__ void append(Cand* buf, Ctl* ctl, float v, int gidx) {
+    int slot = atomicAdd(&ctl->cnt, 1);
+    if (slot < S::CAP) {
+        Cand e;
+        e.key = f2key(v);
+        e.idx = (uint32_t)gidx;
+        buf[slot] = e;
+    }
+}
+
+// One column whose scaled RAW value reached the filter.  The penalty only ever lowers a
+// logit (l/p < l for l > 0, l*p < l for l < 0, p > 1), so filtering raw values first is
+// conservative: only here, on the rare survivor, is the bitmap consulted, the penalty
+// applied and the filter repeated on the true value.
+// A survivor that carries a penalty is rarer still (a column of the history window among the few
+// that pass the filter); its divide lives out of line, once per kernel, so that the streaming
+// loop stays small.  The candidate buffer and the control block sit at fixed offsets.
+template <class S>
+__device__ __noinline__ void penalised_survivor(float raw, int gidx, float thr, bool incl, float inv_temp, float pen) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + 8 * (size_t)S::CAP + 4 * 256);
+    const float v = __fmul_rn(penalise(raw, pen), inv_temp);
+    if (incl ? v >= thr : v > thr) append<S>(buf, ctl, v, gidx);
+}
+template <class S, bool INCL>
+__device__ __forceinline__ void consider(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, float v, int e, float thr) {
+    if (c.pen_bitmap && bm_test(c.bm, e)) {
+        penalised_survivor<S>(raw, e + c.voff, thr, INCL, c.inv_temp, c.pen);
+        return;
+    }
+    append<S>(buf, ctl, v, e + c.voff);
+}
+
+// The largest scaled value of one complete vector, with the penalty applied to the flagged
+// columns: used for the first region only, whose thread-maxima seed the threshold.
+template <typename T>
+__device__ __forceinline__ float vec_max_penalised(const uint4& rawv, int vec, const RowCtx& c) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    const int e0 = vec * VEC - c.mis;
+    float m = __uint_as_float(0xff800000u);
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+        float l = raw[j];
+        if (c.pen_bitmap && bm_test(c.bm, e0 + j)) l = penalise(l, c.pen);
+        m = fmaxf(m, __fmul_rn(l, c.inv_temp));
+    }
+    return m;
+}
+
+// The largest scaled value of one complete vector (no penalty: raw values bound the true ones).
+template <typename T>
+__device__ __forceinline__ float vec_max_scaled(const uint4& rawv, float inv_temp) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    float m = __fmul_rn(raw[0], inv_temp);
+#pragma unroll
+    for (int j = 1; j < VEC; j++) m = fmaxf(m, __fmul_rn(raw[j], inv_temp));
+    return m;
+}
+
+// One complete 16-byte vector that may hold a survivor.  Survivors are walked one at a time
+// (NaN never passes a compare), so the slow code exists once per call site.
+template <class S, typename T, bool INCL>
+__device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const RowCtx& c, float thr, Cand* buf,
+                                           Ctl* ctl) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    uint32_t pass = 0;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+        float x = __fmul_rn(raw[j], c.inv_temp);
+        pass |= (INCL ? x >= thr : x > thr) ? (1u << j) : 0u;
+    }
+    const int e0 = vec * VEC - c.mis;
+    while (pass) {
+        const int j = __ffs(pass) - 1;
+        pass &= pass - 1;
+        float r = raw[0];
+#pragma unroll
+        for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
+        consider<S, INCL>(buf, ctl, c, r, __fmul_rn(r, c.inv_temp), e0 + j, thr);
+    }
+}
+
+// The same three steps for a batch with post-processing: the hot test runs on the raw logits
+// against a raw bound (post_raw_bound), and only a column that passes it pays for the exact value.
+// The exact value of a survivor is a few hundred instructions (two divides, fastExp or tanhf).
+// Inlined at every place a survivor can turn up it made the streaming loop too large for the
+// instruction cache (measured: as many stalls waiting for instructions as at barriers), so it
+// exists once per kernel, out of line, with everything it needs passed by value; the candidate
+// buffer and the control block sit at fixed offsets of the CTA's shared memory.
+template <class S>
+__device__ __noinline__ void post_survivor(float raw, int e, float thr, bool incl, float inv_temp, float pen,
+                                           int voff, int mode, float scale, float cap) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + 8 * (size_t)S::CAP + 4 * 256);
+    const Post post = {mode, scale, cap};
+    float l = post_logit(raw, post);
+    if (pen != 0.0f) l = penalise(l, pen);  // 0: this column carries no penalty
+    const float v = __fmul_rn(l, inv_temp);
+    if (incl ? v >= thr : v > thr) append<S>(buf, ctl, v, e + voff);
+}
+template <class S, bool INCL>
+__device__ __forceinline__ void consider_post(Cand* buf, Ctl* ctl, const RowCtx& c, const Post& post, float raw,
+                                              int e, float thr) {
+    post_survivor<S>(raw, e, thr, INCL, c.inv_temp, (c.pen_bitmap && bm_test(c.bm, e)) ? c.pen : 0.0f, c.voff,
+                     post.mode, post.scale, post.cap);
+}
+
+// The largest raw logit of one complete vector.
+template <typename T>
+__device__ __forceinline__ float vec_max_raw(const uint4& rawv) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    float m = raw[0];
+#pragma unroll
+    for (int j = 1; j < VEC; j++) m = fmaxf(m, raw[j]);
+    return m;
+}
+
+template <class S, typename T, bool INCL>
+__device__ __forceinline__ void filter_vec_post(const uint4& rawv, int vec, const RowCtx& c, const Post& post,
+                                                float rthr, float thr, Cand* buf, Ctl* ctl) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    uint32_t pass = 0;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) pass |= (raw[j] >= rthr) ? (1u << j) : 0u;
+    const int e0 = vec * VEC - c.mis;
+    while (pass) {
+        const int j = __ffs(pass) - 1;
+        pass &= pass - 1;
+        float r = raw[0];
+#pragma unroll
+        for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
+        consider_post<S, INCL>(buf, ctl, c, post, r, e0 + j, thr);
+    }
+}
+
+}  // namespace

@@ -1,0 +1,238 @@
+// Cutting the candidate buffer to its k best entries: the shared-memory radix select, the
+// counting select for small buffers, and the ordering of the survivors.
+// Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
+// translation unit.
+#pragma once
+
+namespace {
+
+// ---------------------------------------------------------------------------------------
+// Shared-memory radix select: cut the candidate buffer to its k best entries in the order
+// (key descending, index ascending).  Called by every thread of the CTA with the buffer
+// quiescent (a barrier after the last append).  Leaves min(k, n) entries, unordered, and
+// returns the key of the k-th one when n > k (*have_kth set).
+//
+// Digits are taken from (key - smallest key), most significant first, so the first
+// histogram already spreads the candidates over up to 256 bins however narrow their
+// value range is.  Ties at the k-th key are resolved by a second select over the index.
+template <class S>
+__device__ __noinline__ uint32_t select_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid, bool* have_kth) {
+    constexpr int NT = S::NT, NWARP = S::NWARP, EPT = S::EPT;
+    const int lane = tid & 31, warp = tid >> 5;
+    __syncthreads();
+    const int n = min(live_count(ctl), S::CAP);
+    __syncthreads();  // every thread has read the count before a caller may append again
+    *have_kth = false;
+    if (n <= k) return 0;
+
+    // range of the keys
+    uint32_t lo = 0xffffffffu, hi = 0;
+    for (int i = tid; i < n; i += NT) {
+        uint32_t key = buf[i].key;
+        lo = min(lo, key);
+        hi = max(hi, key);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    if (lane == 0) {
+        ctl->warpk_min[warp] = lo;
+        ctl->warpk_max[warp] = hi;
+    }
+    __syncthreads();
+    lo = ctl->warpk_min[0];
+    hi = ctl->warpk_max[0];
+#pragma unroll
+    for (int w = 1; w < NWARP; w++) {
+        lo = min(lo, ctl->warpk_min[w]);
+        hi = max(hi, ctl->warpk_max[w]);
+    }
+    const uint32_t range = hi - lo;
+    int rem = range == 0 ? 0 : 32 - __clz(range);  // significant bits of (key - lo)
+
+    int need = k;           // entries wanted among those matching the prefix
+    int ties = n;           // entries matching the whole prefix so far
+    uint32_t prefix = 0;    // chosen high bits of (key - lo)
+    while (rem > 0) {
+        const int d = rem < 8 ? rem : 8;
+        const int shift = rem - d;
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        for (int i = tid; i < n; i += NT) {
+            uint32_t o = buf[i].key - lo;
+            uint32_t hi_bits = rem >= 32 ? 0u : (o >> rem);  // a 32-bit shift by 32 must give 0
+            if (hi_bits == prefix) atomicAdd(&hist[(o >> shift) & ((1u << d) - 1u)], 1u);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane L owns bins 8L..8L+7; find the bin where the count from the top reaches `need`
+            uint32_t c[8];
+            uint32_t tot = 0;
+#pragma unroll
+            for (int b = 0; b < 8; b++) {
+                c[b] = hist[lane * 8 + b];
+                tot += c[b];
+            }
+            uint32_t above = tot;  // inclusive suffix sum over lanes >= me
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t y = __shfl_down_sync(0xffffffffu, above, o);
+                if (lane + o < 32) above += y;
+            }
+            above -= tot;  // exclusive: entries in bins owned by higher lanes
+            if (above < (uint32_t)need && (uint32_t)need <= above + tot) {
+                uint32_t run = above;
+#pragma unroll
+                for (int b = 7; b >= 0; b--) {
+                    if (run < (uint32_t)need && (uint32_t)need <= run + c[b]) {
+                        ctl->sel_bin = lane * 8 + b;
+                        ctl->sel_need = need - (int)run;
+                        ctl->sel_cnt = (int)c[b];
+                    }
+                    run += c[b];
+                }
+            }
+        }
+        __syncthreads();
+        prefix = (prefix << d) | (uint32_t)ctl->sel_bin;
+        need = ctl->sel_need;
+        ties = ctl->sel_cnt;
+        rem = shift;
+    }
+    const uint32_t kth = lo + prefix;
+
+    // `ties` entries carry the k-th key and `need` of them are wanted: the lowest indices.
+    uint32_t idx_max = 0xffffffffu;
+    if (need < ties) {
+        int irem = 32;
+        uint32_t iprefix = 0;
+        int ineed = need;
+        while (irem > 0) {
+            const int shift = irem - 8;
+            if (tid < 256) hist[tid] = 0;
+            __syncthreads();
+            for (int i = tid; i < n; i += NT) {
+                Cand e = buf[i];
+                uint32_t hi_bits = irem >= 32 ? 0u : (e.idx >> irem);
+                if (e.key == kth && hi_bits == iprefix) atomicAdd(&hist[(e.idx >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (warp == 0) {
+                uint32_t c[8];
+                uint32_t tot = 0;
+#pragma unroll
+                for (int b = 0; b < 8; b++) {
+                    c[b] = hist[lane * 8 + b];
+                    tot += c[b];
+                }
+                uint32_t below = tot;  // inclusive prefix sum over lanes <= me
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    uint32_t y = __shfl_up_sync(0xffffffffu, below, o);
+                    if (lane >= o) below += y;
+                }
+                below -= tot;
+                if (below < (uint32_t)ineed && (uint32_t)ineed <= below + tot) {
+                    uint32_t run = below;
+#pragma unroll
+                    for (int b = 0; b < 8; b++) {
+                        if (run < (uint32_t)ineed && (uint32_t)ineed <= run + c[b]) {
+                            ctl->sel_bin = lane * 8 + b;
+                            ctl->sel_need = ineed - (int)run;
+                        }
+                        run += c[b];
+                    }
+                }
+            }
+            __syncthreads();
+            iprefix = (iprefix << 8) | (uint32_t)ctl->sel_bin;
+            ineed = ctl->sel_need;
+            irem = shift;
+        }
+        idx_max = iprefix;  // indices are unique: exactly `need` tied entries have idx <= idx_max
+    }
+
+    // compaction through registers (reads and writes overlap in the buffer)
+    Cand mine[EPT];
+    uint32_t keep = 0;
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        int i = tid + j * NT;
+        if (i < n) {
+            mine[j] = buf[i];
+            if (mine[j].key > kth || (mine[j].key == kth && mine[j].idx <= idx_max)) keep |= 1u << j;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) ctl->cnt = 0;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        if ((keep >> j) & 1u) {
+            int slot = atomicAdd(&ctl->cnt, 1);
+            buf[slot] = mine[j];
+        }
+    }
+    __syncthreads();
+    *have_kth = true;
+    return kth;
+}
+
+// Exact cut for a small buffer (n <= RANK_MAX entries): every entry counts the entries that
+// precede it in the order (key descending, index ascending) and moves to that position,
+// which leaves the best min(k, n) entries in order.  Two barriers, no atomics.
+__device__ __forceinline__ uint32_t rank_select(Cand* buf, Ctl* ctl, int n, int k, int tid, bool* have_kth) {
+    Cand me;
+    me.key = 0;
+    me.idx = 0;
+    int rank = 0x7fffffff;
+    if (tid < n) {
+        me = buf[tid];
+        rank = 0;
+        for (int j = 0; j < n; j++) {
+            Cand o = buf[j];
+            rank += (o.key > me.key || (o.key == me.key && o.idx < me.idx)) ? 1 : 0;
+        }
+    }
+    __syncthreads();
+    if (rank < k) buf[rank] = me;
+    if (rank == k - 1) ctl->sel_bin = (int)me.key;
+    if (tid == 0) ctl->cnt = min(n, k);
+    __syncthreads();
+    *have_kth = n >= k;
+    return (uint32_t)ctl->sel_bin;
+}
+
+// Cut the buffer to its k best entries, by counting when it is small and by radix select
+// otherwise.  Called by every thread with the buffer quiescent.
+template <class S>
+__device__ __forceinline__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid,
+                                                 bool* have_kth, bool* ordered = nullptr) {
+    __syncthreads();
+    const int n = live_count(ctl);
+    __syncthreads();
+    if (ordered) *ordered = n <= RANK_MAX;  // the counting select leaves its survivors in order
+    if (n <= RANK_MAX) return rank_select(buf, ctl, n, k, tid, have_kth);
+    return select_topk<S>(buf, ctl, hist, k, tid, have_kth);
+}
+
+// Orders the n <= KCAP entries of the buffer (key descending, index ascending) by
+// counting, into sval/sidx.  Entries are distinct under that order, so ranks are a
+// permutation.
+template <class S>
+__device__ void rank_sort(const Cand* buf, int n, float* sval, int32_t* sidx, int tid) {
+    for (int i = tid; i < n; i += S::NT) {
+        Cand me = buf[i];
+        int rank = 0;
+        for (int j = 0; j < n; j++) {
+            Cand o = buf[j];
+            rank += (o.key > me.key || (o.key == me.key && o.idx < me.idx)) ? 1 : 0;
+        }
+        sval[rank] = key2f(me.key);
+        sidx[rank] = (int32_t)me.idx;
+    }
+}
+
+}  // namespace

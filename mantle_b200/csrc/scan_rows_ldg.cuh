@@ -1,0 +1,287 @@
+// scan_rows_ldg_kernel: the streaming pass with plain 16-byte loads; the default kernel.
+// Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
+// translation unit.
+#pragma once
+
+namespace {
+
+// ---------------------------------------------------------------------------------------
+// The same streaming pass with plain 16-byte loads instead of the bulk-copy ring: one CTA per
+// item (row, split), two register sets per thread, each refilled from global memory while the
+// other is filtered, one barrier per region of NT*U vectors.  No shared-memory staging, so the
+// CTA is small (candidate buffer + bitmap) and four of them share an SM; which of the two
+// kernels is faster for a batch is a matter of measurement (see launch_scan).
+
+template <class S>
+struct LdgLayout {
+    // shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [bitmap words]
+    static constexpr size_t FIXED = 8 * (size_t)S::CAP + 4 * 256 + 512;
+};
+
+template <class S, typename T, int MODE, bool POST>
+__global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KArgs a) {
+    constexpr int VEC = Elem<T>::VEC;
+    constexpr int NT = S::NT, NWARP = S::NWARP, U = S::U, CAP = S::CAP;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(buf + CAP);
+    Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
+    uint32_t* bm = reinterpret_cast<uint32_t*>(smem_raw + LdgLayout<S>::FIXED);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int item = blockIdx.x;
+    const int row = item / a.splits;
+    const int split = item - row * a.splits;
+
+    const MantleSampleParams P = row_params(a, row);
+    bool greedy, bad_k;
+    const int k = row_k(a, P, S::KCAP, &greedy, &bad_k);
+    const ItemGeom<T, S> g = item_geom<T, S>(a, item);
+
+    RowCtx c;
+    c.row = g.row;
+    c.mis = g.mis;
+    c.V = a.vocab;
+    c.voff = a.vocab_offset;
+    c.inv_temp = greedy ? 1.0f : __fdiv_rn(1.0f, P.temperature);  // sampler.go:144-145
+    c.pen = P.repeat_penalty;
+    c.bm = bm;
+    c.pen_bitmap = false;
+    const uint4* vbase = g.vbase;
+    const int a0 = g.a0, b0 = g.b0, elo = g.elo, ehi = g.ehi;
+    constexpr int RV = NT * U;  // vectors per region
+    const int nreg = g.nchunks;
+    bool careful = k > 32 * NWARP;
+
+    // The first region's loads go out before anything else: they are in flight while the bitmap is built.
+    uint4 ra[U], rb[U];
+    auto load = [&](uint4(&dst)[U], int r) {  // region r (only the last region can be partial)
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            int v = a0 + r * RV + u * NT + tid;
+            // the zero fill is not read (the tests below mask what lies beyond the item), but a load
+            // that kept the register's old value would have to wait for its last reader (measured: 1.6 % slower)
+            dst[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    // `ahead(r)`: ask the L2 for region r (one request per 128-byte line), two regions before its
+    // loads are issued, so that those loads find their lines on the way or already there
+    auto ahead = [&](int r) {
+#if LDG_PREFETCH
+        // a warp's share of a region is U runs of 512 bytes: lane i asks for line i & 3 of run i >> 2
+        if (r < nreg && lane < 4 * U) {
+            const int v = a0 + r * RV + (lane >> 2) * NT + (tid & ~31) + (lane & 3) * 8;
+            if (v < b0) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(vbase + v));
+        }
+#endif
+    };
+    if (!careful && nreg > 0) {
+        load(ra, 0);
+        ahead(1);
+        ahead(2);
+    }
+    if (tid == 0) ctl->cnt = 0;
+
+    // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
+    const int hl = history_len(a, row);
+    WinPlan wp = win_plan(a, P, hl);
+    wp.staged = false;
+    if (wp.active) {
+        build_penalty_bitmap_early<NT>(a, row, wp, hl, c.V, c.voff, bm, tid);
+        c.pen_bitmap = true;
+    }
+    __syncthreads();
+
+    // ---- stream the item ------------------------------------------------------------------
+    const int trig = min(k + max(k >> 1, 16), CAP / 2);  // cut the buffer at this many entries
+    float thr = __uint_as_float(0xff800000u);            // -inf
+    float rthr = thr;  // POST: the raw logit every column that can reach thr has at least
+    const Post& POSTP = a.post;
+
+    if (!careful && nreg > 0) {
+        // later regions: the buffer already holds k entries >= thr with lower indices, so an equal
+        // value can no longer enter (sampler.go:268-275); one test per thread and region
+        auto later = [&](const uint4(&src)[U], int r) {
+            const int v0 = a0 + r * RV + tid;
+            const bool whole = r + 1 < nreg;
+            float mu[U];
+            float m = __uint_as_float(0xff800000u);
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                mu[u] = __uint_as_float(0x7fc00000u);  // NaN: beyond the item, admitted by no compare
+                if (whole || v0 + u * NT < b0)
+                    mu[u] = POST ? vec_max_raw<T>(src[u]) : vec_max_scaled<T>(src[u], c.inv_temp);
+                m = fmaxf(m, mu[u]);
+            }
+            if (POST) {
+                if (m >= rthr) {
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+                        if (mu[u] >= rthr) filter_vec_post<S, T, false>(src[u], v0 + u * NT, c, POSTP, rthr, thr, buf, ctl);
+                }
+            } else if (m > thr) {
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (mu[u] > thr) filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
+            }
+        };
+        // one barrier per region; the thread that made the region's last append reads the final
+        // count before it arrives, so the OR is the same for every thread
+        auto region_end = [&](int lim) {
+            if (__syncthreads_or(live_count(ctl) >= lim)) {
+                if (live_count(ctl) > CAP) {
+                    careful = true;  // entries were dropped: redo the item on the careful path
+                } else {
+                    bool have;
+                    uint32_t kth = refresh_topk<S>(buf, ctl, hist, k, tid, &have);
+                    if (have) {
+                        thr = key2f(kth);
+                        if (POST) rthr = post_raw_bound(thr, c.inv_temp, POSTP);
+                    }
+                }
+            }
+        };
+
+        // -- region 0 seeds the threshold (see scan_rows_kernel) --
+        if (nreg > 1) load(rb, 1);
+        {
+            const int v0 = a0 + tid;
+            // Thread maxima of the RAW logits: everything between a raw logit and its final value
+            // (post-processing up to its slack, penalty, temperature) is non-decreasing, and a
+            // column's value is at least what it would be with the penalty, so the image of a raw
+            // logit that k columns reach is a value that k columns reach -- no bitmap lookups here.
+            float tmax = __uint_as_float(0xff800000u);
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (v0 + u * NT < b0) tmax = fmaxf(tmax, vec_max_raw<T>(ra[u]));
+            float x = tmax;  // bitonic sort across the warp, descending
+#pragma unroll
+            for (int k2 = 2; k2 <= 32; k2 <<= 1) {
+#pragma unroll
+                for (int j2 = k2 >> 1; j2 > 0; j2 >>= 1) {
+                    float y = __shfl_xor_sync(0xffffffffu, x, j2);
+                    bool desc = (lane & k2) == 0;
+                    bool lower = (lane & j2) == 0;
+                    x = (lower == desc) ? fmaxf(x, y) : fminf(x, y);
+                }
+            }
+            const int j = (k + NWARP - 1) / NWARP;
+            float wj = __shfl_sync(0xffffffffu, x, j - 1);
+            if (lane == 0) ctl->warpv[warp] = wj;
+            __syncthreads();
+            float t0 = ctl->warpv[0];
+#pragma unroll
+            for (int w = 1; w < NWARP; w++) t0 = fminf(t0, ctl->warpv[w]);
+            if (POST) t0 = post_seed_logit(t0, POSTP);
+            if (c.pen_bitmap) t0 = penalise(t0, c.pen);
+            t0 = __fmul_rn(t0, c.inv_temp);
+            if (POST) {
+                thr = t0;
+                rthr = post_raw_bound(thr, c.inv_temp, POSTP);
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (v0 + u * NT < b0) filter_vec_post<S, T, true>(ra[u], v0 + u * NT, c, POSTP, rthr, thr, buf, ctl);
+            } else {
+                thr = t0;
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (v0 + u * NT < b0) filter_vec<S, T, true>(ra[u], v0 + u * NT, c, thr, buf, ctl);
+            }
+        }
+        region_end(k + 1);
+
+        // -- regions 1.. : two register sets, each refilled while the other is filtered --
+        // The barrier carries only the vote (the register sets are private), so it need not follow
+        // every region: the threshold is refreshed at most every LDG_VOTE_EVERY regions, at the
+        // price of a few more survivors under a threshold that is that much staler.
+        int r = 1;
+        while (r < nreg && !careful) {
+            if (r + 1 < nreg) load(ra, r + 1);
+            ahead(r + 3);
+            later(rb, r);
+            if (r % LDG_VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
+            if (++r >= nreg || careful) break;
+            if (r + 1 < nreg) load(rb, r + 1);
+            ahead(r + 3);
+            later(ra, r);
+            if (r % LDG_VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
+            ++r;
+        }
+    }
+
+    if (!careful) {
+        // the columns of the partial vectors at the ends of this item
+        int r1_lo = elo, r1_hi = ehi, r2_lo = ehi, r2_hi = ehi;
+        if (b0 > a0) {
+            r1_hi = min(ehi, max(elo, a0 * VEC - c.mis));
+            r2_lo = max(elo, b0 * VEC - c.mis);
+        }
+        const int n1 = r1_hi - r1_lo, n2 = r2_hi - r2_lo;
+        if (tid < n1 + n2) {  // at most 4 * VEC columns
+            int e = tid < n1 ? r1_lo + tid : r2_lo + (tid - n1);
+            float raw = Elem<T>::load1(c.row, e);
+            if (POST) {
+                if (raw >= rthr) consider_post<S, true>(buf, ctl, c, POSTP, raw, e, thr);
+            } else {
+                float v = __fmul_rn(raw, c.inv_temp);
+                if (v >= thr) consider<S, true>(buf, ctl, c, raw, v, e, thr);
+            }
+        }
+        __syncthreads();
+        if (live_count(ctl) > CAP) careful = true;
+        __syncthreads();
+    }
+
+    if (careful) {  // the careful path of scan_rows_kernel
+        __syncthreads();
+        if (tid == 0) ctl->cnt = 0;
+        __syncthreads();
+        thr = __uint_as_float(0xff800000u);
+        bool strict = false;
+        constexpr int STEP = NT * S::SLOW_EPT;
+        for (int e0 = elo; e0 < ehi; e0 += STEP) {
+            __syncthreads();
+            if (ctl->cnt + STEP > CAP) {
+                bool have;
+                uint32_t kth = select_topk<S>(buf, ctl, hist, k, tid, &have);
+                if (have) {
+                    thr = key2f(kth);
+                    strict = true;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < S::SLOW_EPT; j++) {
+                int e = e0 + j * NT + tid;
+                if (e < ehi) {
+                    float l = Elem<T>::load1(c.row, e);
+                    if (POST) l = post_logit(l, POSTP);
+                    if (c.pen_bitmap && bm_test(bm, e)) l = penalise(l, c.pen);
+                    float v = __fmul_rn(l, c.inv_temp);
+                    if (strict ? (v > thr) : (v >= thr)) append<S>(buf, ctl, v, e + c.voff);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    bool have, ordered;
+    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
+    __syncthreads();
+    if (bad_k) {
+        if (tid == 0) {
+            if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_TOPK_RANGE);
+            if (MODE == MODE_FUSED) {
+                a.next[row] = -1;
+                if (a.n_kept) a.n_kept[row] = 0;
+                if (a.cut) a.cut[row] = 0;
+            } else {
+                a.part_cnt[(size_t)split * a.rows + row] = 0;
+            }
+        }
+        return;
+    }
+    finish_row<S, MODE>(a, row, split, P, greedy, ordered, buf, ctl, tid);
+}
+
+}  // namespace
