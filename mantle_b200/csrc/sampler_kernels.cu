@@ -128,7 +128,7 @@ bool use_small_shape(int max_top_k) {
 
 // Which streaming kernel serves a batch: plain loads, unless MANTLE_SAMPLER_KERNEL=tma asks for
 // the bulk-copy ring (which has no post-processing form).  Measured on 151 936-column float32
-// rows, plain loads against the ring: 0.437 against 0.541 ms for 4096 rows at top_k 20;
+// rows, plain loads against the ring: 0.403 against 0.541 ms for 4096 rows at top_k 20;
 // 0.93 against 1.06 ms (top_k 300), 1.22 against 1.46 ms (512), 3.70 against 3.86 ms (1024)
 // for 2048 rows.
 bool use_ldg(int max_top_k, bool post) {

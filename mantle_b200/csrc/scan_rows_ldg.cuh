@@ -55,12 +55,14 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
 
     // The first region's loads go out before anything else: they are in flight while the bitmap is built.
     uint4 ra[U], rb[U];
-    auto load = [&](uint4(&dst)[U], int r) {  // region r (only the last region can be partial)
+    // Only an item's last region can be partial.  Measured alternatives, each with fewer instructions
+    // and each slower: loads that leave a register beyond the item as it is (they wait for its last
+    // reader, 1.6 %), loads without bounds tests for whole regions (2 %), a -inf fill that spares the
+    // masks below (1 %).
+    auto load = [&](uint4(&dst)[U], int r) {
 #pragma unroll
         for (int u = 0; u < U; u++) {
             int v = a0 + r * RV + u * NT + tid;
-            // the zero fill is not read (the tests below mask what lies beyond the item), but a load
-            // that kept the register's old value would have to wait for its last reader (measured: 1.6 % slower)
             dst[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
         }
     };
@@ -103,14 +105,13 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         // value can no longer enter (sampler.go:268-275); one test per thread and region
         auto later = [&](const uint4(&src)[U], int r) {
             const int v0 = a0 + r * RV + tid;
-            const bool whole = r + 1 < nreg;
             float mu[U];
             float m = __uint_as_float(0xff800000u);
+            const bool whole = r + 1 < nreg;
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 mu[u] = __uint_as_float(0x7fc00000u);  // NaN: beyond the item, admitted by no compare
-                if (whole || v0 + u * NT < b0)
-                    mu[u] = POST ? vec_max_raw<T>(src[u]) : vec_max_scaled<T>(src[u], c.inv_temp);
+                if (whole || v0 + u * NT < b0) mu[u] = vec_max_raw<T>(src[u]);
                 m = fmaxf(m, mu[u]);
             }
             if (POST) {
@@ -119,10 +120,13 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                     for (int u = 0; u < U; u++)
                         if (mu[u] >= rthr) filter_vec_post<S, T, false>(src[u], v0 + u * NT, c, POSTP, rthr, thr, buf, ctl);
                 }
-            } else if (m > thr) {
+            } else if (__fmul_rn(m, c.inv_temp) > thr) {
+                // A rounded multiply by a positive factor is non-decreasing, so the largest scaled value
+                // is the scaled largest raw value, exactly: one multiply per thread and region here,
+                // one per vector below, and the sixteen only where a vector holds a survivor.
 #pragma unroll
                 for (int u = 0; u < U; u++)
-                    if (mu[u] > thr) filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
+                    if (__fmul_rn(mu[u], c.inv_temp) > thr) filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
             }
         };
         // one barrier per region; the thread that made the region's last append reads the final
