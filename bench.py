@@ -393,8 +393,8 @@ def run_vocab_sharded(args, world, rank, device):
     hist = torch.randint(0, V, (rows, 512), generator=torch.Generator().manual_seed(7), dtype=torch.int32).to(device)
     p_dev = sampler.params_to_device(ref.params, device)
 
-    def step():
-        return sharded.sample_vocab_sharded(w.logits, p_dev, w.max_top_k, V, history=hist)
+    plan = sharded.VocabShardedPlan(w.logits, p_dev, w.max_top_k, V, history=hist)
+    step = plan.step
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -408,10 +408,10 @@ def run_vocab_sharded(args, world, rank, device):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "vocab_sharded: %d rows x 262144 f32 columns over %d GPU(s) (%d columns each), "
                                    "top_k 50 top_p 0.95 temp 0.7 repeat_penalty 1.15, history 512 ids; local top-k, "
-                                   "NCCL all-gather of the shortlists, merge" % (rows, world, width),
+                                   "one NCCL all-gather of the packed shortlists, merge" % (rows, world, width),
                        "l2": "per-GPU inputs of %.0f MB; L2-resident below 126 MB" % (scan_bytes / 1e6)},
             "roofline": {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
-                         "note": "latency-bound: three launches and one collective per step"},
+                         "note": "latency-bound: two launches and one collective per step"},
             "gpu_launches": args.steps * 2,
         }
         print(json.dumps(line), flush=True)

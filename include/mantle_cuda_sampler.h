@@ -204,6 +204,18 @@ int mantleCudaSampleMergeParts(const MantleSampleBatch* batch, int parts, const 
                                mantleCudaStream_t stream);
 
 /*
+ * The same merge for shortlists that travel as one block per rank, so that one all-gather
+ * carries a step: a block is [rows * part_cap float values][rows * part_cap int32 ids]
+ * [rows int32 counts], mantleCudaSamplePackedPartBytes() bytes long (padded to 256); `packed`
+ * holds `parts` blocks in rank order.  A rank fills its block with
+ * mantleCudaSampleLocalTopK(..., block, block + rows * part_cap, block + 2 * rows * part_cap, ...)
+ * (pointers in 4-byte elements).
+ */
+int mantleCudaSamplePackedPartBytes(int rows, int part_cap, size_t* bytes);
+int mantleCudaSampleMergePacked(const MantleSampleBatch* batch, int parts, const void* packed, int part_cap,
+                                mantleCudaStream_t stream);
+
+/*
  * Sampler.Sample for a batch that lives in HOST memory: the form of the reference's
  * call site, where the logits arrive as a host slice (internal/inference/engine.go:233,
  * 279, 296 pass `logitsVec []float32`).  Every pointer of `host_batch` (logits, history,

@@ -24,10 +24,9 @@ __global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_part
     if (tid == 0) ctl->cnt = 0;
     __syncthreads();
     for (int p = 0; p < a.parts; p++) {
-        const size_t slot = (size_t)p * a.rows + row;
-        const int m = min(a.part_cnt[slot], a.part_cap);
-        for (int i = tid; i < m; i += S::NT)
-            append<S>(buf, ctl, a.part_val[slot * a.part_cap + i], a.part_idx[slot * a.part_cap + i]);
+        const size_t at = (size_t)p * (size_t)a.part_stride + (size_t)row * a.part_cap;
+        const int m = min(a.part_cnt[(size_t)p * (size_t)a.cnt_stride + row], a.part_cap);
+        for (int i = tid; i < m; i += S::NT) append<S>(buf, ctl, a.part_val[at + i], a.part_idx[at + i]);
     }
     if (bad_k) {
         if (tid == 0) {

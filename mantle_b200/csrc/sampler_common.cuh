@@ -135,6 +135,8 @@ struct KArgs {
     int32_t* part_idx;
     int32_t* part_cnt;
     int part_cap;
+    long long part_stride;  // elements from one part's values (ids) to the next part's: rows * part_cap unless packed
+    long long cnt_stride;   // the same for the counts: rows unless packed
     int parts;
     int hist_tma_ok;  // history base 16-byte aligned and hist_stride a multiple of 4
     Post post;  // read from the kernel's parameter space where it is used, never copied to registers

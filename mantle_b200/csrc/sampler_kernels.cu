@@ -221,6 +221,8 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
     a.part_idx = nullptr;
     a.part_cnt = nullptr;
     a.part_cap = 0;
+    a.part_stride = 0;
+    a.cnt_stride = 0;
     a.parts = 0;
     a.hist_tma_ok = a.history && reinterpret_cast<uintptr_t>(a.history) % 16 == 0 && a.hist_stride % 4 == 0;
     a.post.mode = post_mode_of(b->logit_scale, b->logit_softcap, b->flags);
@@ -288,7 +290,9 @@ int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
     return launch_scan_shape<ShapeLargeK, MODE>(a, dtype, stream);
 }
 
-int launch_merge(const KArgs& a, cudaStream_t stream) {
+int launch_merge(KArgs& a, cudaStream_t stream) {
+    if (a.part_stride == 0) a.part_stride = (long long)a.rows * a.part_cap;
+    if (a.cnt_stride == 0) a.cnt_stride = a.rows;
     const size_t smem = ShapeLargeK::SMEM_FIXED;
     cudaError_t e = cudaFuncSetAttribute(merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -448,6 +452,39 @@ extern "C" int mantleCudaSampleLocalTopK(const MantleSampleBatch* batch, int voc
     int rc = apply_write_back(a, static_cast<cudaStream_t>(stream_));
     if (rc) return rc;
     return launch_scan<MODE_PARTS>(a, batch->dtype, static_cast<cudaStream_t>(stream_));
+}
+
+// One rank's shortlists as one block, so that a single all-gather moves everything:
+// [rows * cap float values][rows * cap int32 ids][rows int32 counts], padded to 256 bytes.
+static size_t packed_part_bytes(int rows, int cap) {
+    const size_t b = ((size_t)rows * cap * 2 + (size_t)rows) * 4;
+    return (b + 255) & ~(size_t)255;
+}
+
+extern "C" int mantleCudaSamplePackedPartBytes(int rows, int part_cap, size_t* bytes) {
+    if (!bytes || rows <= 0 || part_cap <= 0) return kInvalid;
+    *bytes = packed_part_bytes(rows, part_cap);
+    return 0;
+}
+
+extern "C" int mantleCudaSampleMergePacked(const MantleSampleBatch* batch, int parts, const void* packed, int part_cap,
+                                           mantleCudaStream_t stream_) {
+    if (!batch || batch->rows <= 0 || !batch->params || !batch->next || batch->vocab <= 0) return kInvalid;
+    if (batch->max_top_k < 1 || batch->max_top_k > KMAX) return kInvalid;
+    if ((batch->cand_idx || batch->cand_prob) && batch->cand_stride <= 0) return kInvalid;
+    if (parts < 1 || !packed || part_cap < 1 || reinterpret_cast<uintptr_t>(packed) % 16) return kInvalid;
+    if ((long long)parts * (part_cap < batch->max_top_k ? part_cap : batch->max_top_k) > MERGE_CAP) return kInvalid;
+    KArgs a;
+    fill_args(a, batch);
+    const size_t n = (size_t)batch->rows * part_cap;
+    a.parts = parts;
+    a.part_cap = part_cap;
+    a.part_val = const_cast<float*>(static_cast<const float*>(packed));
+    a.part_idx = reinterpret_cast<int32_t*>(a.part_val + n);
+    a.part_cnt = a.part_idx + n;
+    a.part_stride = (long long)(packed_part_bytes(batch->rows, part_cap) / 4);
+    a.cnt_stride = a.part_stride;
+    return launch_merge(a, static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int mantleCudaSampleMergeParts(const MantleSampleBatch* batch, int parts, const float* part_val,

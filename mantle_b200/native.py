@@ -90,6 +90,8 @@ EXPORTS = {
         C.c_int,
         [C.POINTER(SampleBatch), C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p],
     ),
+    "mantleCudaSamplePackedPartBytes": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_size_t)]),
+    "mantleCudaSampleMergePacked": (C.c_int, [C.POINTER(SampleBatch), C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "mantleCudaSampleRowsHost": (C.c_int, [C.POINTER(SampleBatch), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mantleCudaSamplerHostWorkspaceBytes": (C.c_int, [C.POINTER(SampleBatch), C.POINTER(C.c_size_t)]),
     "mantleCudaSampleRowsNoAlloc": (C.c_int, [C.POINTER(SampleBatch), C.c_void_p]),

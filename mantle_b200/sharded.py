@@ -48,6 +48,93 @@ def gather_parts(val, idx, cnt, group=None):
     return g_val, g_idx, g_cnt
 
 
+def packed_part_bytes(rows, cap):
+    """Bytes of one rank's block: [rows*cap float values][rows*cap int32 ids][rows int32 counts],
+    padded to 256 (mantleCudaSamplePackedPartBytes)."""
+    return ((rows * cap * 2 + rows) * 4 + 255) & ~255
+
+
+def packed_part_views(block, rows, cap):
+    """(val [rows, cap] float32, idx [rows, cap] int32, cnt [rows] int32) views into one block
+    (a uint8 tensor of packed_part_bytes(rows, cap) bytes)."""
+    words = block.view(torch.int32)
+    n = rows * cap
+    return words[:n].view(torch.float32).view(rows, cap), words[n:2 * n].view(rows, cap), words[2 * n:2 * n + rows]
+
+
+class VocabShardedPlan:
+    """A vocabulary-sharded batch bound to its buffers: build once, step many times.
+
+    A step is the local shortlist kernel writing this rank's block, ONE all-gather of the blocks,
+    and the merge kernel; nothing is allocated per step."""
+
+    def __init__(self, local_logits, params_dev, max_top_k, vocab_total, history=None, hist_len=None, exclude=None,
+                 cand_cap=0, group=None):
+        from . import native, sampler
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.offset, width = vocab_shard(vocab_total, self.world, self.rank)
+        if local_logits.shape[1] != width:
+            raise ValueError("rank %d holds %d columns, its share of %d is %d"
+                             % (self.rank, local_logits.shape[1], vocab_total, width))
+        self.lib = native.load()
+        self.sampler = sampler
+        self.native = native
+        dev = local_logits.device
+        rows = local_logits.shape[0]
+        self.rows, self.k, self.vocab_total = rows, max_top_k, vocab_total
+        self.keep = [local_logits, params_dev, history, hist_len, exclude]
+        nbytes = packed_part_bytes(rows, max_top_k)
+        self.block = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        self.gathered = torch.zeros(self.world * nbytes, dtype=torch.uint8, device=dev)
+        self.val, self.idx, self.cnt = packed_part_views(self.block, rows, max_top_k)
+        import ctypes as C
+
+        b = native.SampleBatch()
+        b.logits = local_logits.data_ptr()
+        b.dtype = native.DTYPE_F32 if local_logits.dtype == torch.float32 else native.DTYPE_BF16
+        b.rows, b.vocab, b.max_top_k, b.row_stride = rows, width, max_top_k, local_logits.stride(0)
+        if history is not None and history.numel() > 0:
+            b.history, b.hist_stride = history.data_ptr(), history.shape[1]
+            if hist_len is not None:
+                b.hist_len = hist_len.data_ptr()
+        if exclude is not None and exclude.numel() > 0:
+            b.exclude, b.n_exclude = exclude.data_ptr(), exclude.numel()
+        b.params = params_dev.data_ptr()
+        self.local = b
+        out = sampler.SampleOutputs()
+        out.next = torch.full((rows,), -2, dtype=torch.int32, device=dev)
+        out.cand_idx = torch.full((rows, cand_cap), -1, dtype=torch.int32, device=dev) if cand_cap else None
+        out.cand_prob = torch.zeros((rows, cand_cap), dtype=torch.float64, device=dev) if cand_cap else None
+        out.n_kept = torch.zeros(rows, dtype=torch.int32, device=dev)
+        out.cut = torch.zeros(rows, dtype=torch.int32, device=dev)
+        out.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.out = out
+        m = native.SampleBatch()
+        m.rows, m.vocab, m.max_top_k = rows, vocab_total, max_top_k
+        m.params, m.next = params_dev.data_ptr(), out.next.data_ptr()
+        if cand_cap:
+            m.cand_idx, m.cand_prob, m.cand_stride = out.cand_idx.data_ptr(), out.cand_prob.data_ptr(), cand_cap
+        m.n_kept, m.cut, m.status = out.n_kept.data_ptr(), out.cut.data_ptr(), out.status.data_ptr()
+        self.merge = m
+        self.C = C
+
+    def step(self):
+        """Queues one sampling step on torch's current stream; every rank gets the same tokens."""
+        C, native = self.C, self.native
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: C.c_void_p(t.data_ptr())
+        rc = self.lib.mantleCudaSampleLocalTopK(C.byref(self.local), self.offset, self.vocab_total, p(self.val),
+                                                p(self.idx), p(self.cnt), self.k, stream)
+        native.check(rc, "mantleCudaSampleLocalTopK")
+        dist.all_gather_into_tensor(self.gathered, self.block, group=self.group)
+        rc = self.lib.mantleCudaSampleMergePacked(C.byref(self.merge), self.world, p(self.gathered), self.k, stream)
+        native.check(rc, "mantleCudaSampleMergePacked")
+        return self.out
+
+
 def sample_vocab_sharded(local_logits, params_dev, max_top_k, vocab_total, history=None, hist_len=None,
                          exclude=None, cand_cap=0, group=None):
     """One sampling step over vocabulary-sharded logits.  Every rank returns the same tokens.

@@ -35,6 +35,14 @@ def _rank_main(rank, world, port, tmp):
         ref = O.sample_rows(w.logits.numpy().copy(), w.params, history=w.history.numpy(), cand_cap=50)
         compare(gpu, ref, 50, where="rank %d" % rank)
         assert int(out.status.item()) == 0
+        # the same step through one packed all-gather, twice in a row on the same buffers
+        plan = sharded.VocabShardedPlan(local, p_dev, w.max_top_k, V, history=w.history.to(dev), cand_cap=50)
+        for _ in range(2):
+            o2 = plan.step()
+            torch.cuda.synchronize()
+            gpu2 = dict(next=o2.next.cpu().numpy(), n_kept=o2.n_kept.cpu().numpy(), cut=o2.cut.cpu().numpy(),
+                        cand_idx=o2.cand_idx.cpu().numpy(), cand_prob=o2.cand_prob.cpu().numpy())
+            compare(gpu2, ref, 50, where="packed, rank %d" % rank)
         open(os.path.join(tmp, "ok%d" % rank), "w").write("ok")
     finally:
         dist.destroy_process_group()

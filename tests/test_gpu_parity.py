@@ -293,6 +293,40 @@ def test_vocab_sharded_on_one_gpu():
     compare(gpu, ref, 50)
 
 
+def test_vocab_sharded_packed_blocks_on_one_gpu():
+    """The same eight shards written into one packed block each (what a single all-gather moves)
+    and merged by mantleCudaSampleMergePacked."""
+    from mantle_b200 import sharded
+
+    w = workloads.make("vocab_sharded", rows=64, device=DEV)
+    V, G, k, rows = w.vocab, 8, w.max_top_k, 64
+    p_dev = sampler.params_to_device(w.params, DEV)
+    lib = native.load()
+    nbytes = C.c_size_t(0)
+    assert lib.mantleCudaSamplePackedPartBytes(rows, k, C.byref(nbytes)) == 0
+    assert nbytes.value == sharded.packed_part_bytes(rows, k)
+    gathered = torch.zeros(G * nbytes.value, dtype=torch.uint8, device=DEV)
+    for g in range(G):
+        lo = g * (V // G)
+        shard = w.logits[:, lo:lo + V // G].contiguous()
+        v, i, c = sampler.local_topk(shard, p_dev, k, lo, V, history=w.history)
+        bv, bi, bc = sharded.packed_part_views(gathered[g * nbytes.value:(g + 1) * nbytes.value], rows, k)
+        bv.copy_(v), bi.copy_(i), bc.copy_(c)
+    nxt = torch.full((rows,), -2, dtype=torch.int32, device=DEV)
+    n_kept = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    cut = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    b = native.SampleBatch()
+    b.rows, b.vocab, b.max_top_k = rows, V, k
+    b.params, b.next, b.n_kept, b.cut = p_dev.data_ptr(), nxt.data_ptr(), n_kept.data_ptr(), cut.data_ptr()
+    rc = lib.mantleCudaSampleMergePacked(C.byref(b), G, C.c_void_p(gathered.data_ptr()), k,
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    ref = O.sample_rows(w.logits.cpu().numpy(), w.params, history=w.history.cpu().numpy())
+    assert np.array_equal(nxt.cpu().numpy(), ref["next"])
+    assert np.array_equal(n_kept.cpu().numpy(), ref["n_kept"]) and np.array_equal(cut.cpu().numpy(), ref["cut"])
+
+
 # ---- errors -------------------------------------------------------------------------------------------------
 
 def test_top_k_beyond_bound_sets_status():

@@ -62,6 +62,17 @@ def _rank_main(rank, world, port, tmp):
             want_i, want_v = O.topk(logits[r], k, inv_temp)
             assert [c[1] for c in cand[:k]] == want_i.tolist(), (rank, r)
             assert [np.float32(c[0]) for c in cand[:k]] == want_v.tolist()
+        # the same through one block per rank and ONE all-gather (the layout the packed merge reads)
+        nbytes = sharded.packed_part_bytes(rows, k)
+        assert nbytes % 256 == 0 and nbytes >= (2 * rows * k + rows) * 4
+        block = torch.zeros(nbytes, dtype=torch.uint8)
+        b_val, b_idx, b_cnt = sharded.packed_part_views(block, rows, k)
+        b_val.copy_(torch.from_numpy(val)); b_idx.copy_(torch.from_numpy(idx)); b_cnt.copy_(torch.from_numpy(cnt))
+        gathered = torch.zeros(world * nbytes, dtype=torch.uint8)
+        dist.all_gather_into_tensor(gathered, block)
+        for p in range(world):
+            pv, pi, pc = sharded.packed_part_views(gathered[p * nbytes:(p + 1) * nbytes], rows, k)
+            assert torch.equal(pv, g_val[p]) and torch.equal(pi, g_idx[p]) and torch.equal(pc, g_cnt[p])
         open(os.path.join(tmp, "ok%d" % rank), "w").write("ok")
     finally:
         dist.destroy_process_group()
