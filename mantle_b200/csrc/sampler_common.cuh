@@ -426,6 +426,19 @@ __device__ __forceinline__ float vec_max_raw(const uint4& rawv) {
     for (int j = 1; j < VEC; j++) m = fmaxf(m, raw[j]);
     return m;
 }
+// bfloat16: the eight values are compared as four packed pairs (three two-wide maxima) and only
+// the winning pair is widened -- six instructions instead of fifteen.  Like fmaxf, the packed
+// maximum returns the other operand when one is NaN, and -0.0 against +0.0 may return either,
+// which no compare downstream can tell apart.
+template <>
+__device__ __forceinline__ float vec_max_raw<bf16_t>(const uint4& rawv) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&rawv.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&rawv.y);
+    const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&rawv.z);
+    const __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162*>(&rawv.w);
+    const __nv_bfloat162 m2 = __hmax2(__hmax2(a, b), __hmax2(c, d));
+    return fmaxf(__low2float(m2), __high2float(m2));
+}
 
 template <class S, typename T, bool INCL>
 __device__ __forceinline__ void filter_vec_post(const uint4& rawv, int vec, const RowCtx& c, const Post& post,

@@ -21,6 +21,7 @@
 // Arithmetic contract: every float32 and float64 operation the reference performs is
 // issued as a round-to-nearest intrinsic so nothing is contracted into an FMA.
 
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
