@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import oracle_lib as O
-from gpu_util import check_against_oracle, run_gpu
+from gpu_util import check_against_oracle, compare, run_gpu
 from mantle_b200 import native, sampler, workloads
 from test_gpu_parity import random_params
 
@@ -142,3 +142,23 @@ def test_fused_vocabulary_shards():
     out = sampler.merge_parts(p_dev, k, V, val, idx, cnt)
     torch.cuda.synchronize()
     assert np.array_equal(out.next.cpu().numpy(), ref["next"])
+
+
+def test_fused_unaligned_rows_and_forced_splits():
+    """Rows that start off a 16-byte boundary, a padded stride whose padding must never be read,
+    and rows forced over several CTAs, all with post-processing."""
+    rng = np.random.default_rng(81)
+    for V, stride in [(9999, 9999), (10001, 10003), (151937, 151937)]:
+        rows = 7
+        full = (rng.standard_normal((rows, stride)) * 6).astype(np.float32)
+        full[:, V:] = 1e30
+        params = random_params(rng, rows, ks=(1, 20, 200))
+        hist = rng.integers(0, V, size=(rows, 64)).astype(np.int32)
+        ref_logits = O.postprocess(full[:, :V].copy(), 0.75, 12.0)  # a copy: the device gets the raw logits
+        ref = O.sample_rows(ref_logits, params, history=hist, cand_cap=200)
+        for splits in (1, 3, 0):
+            dev = torch.from_numpy(full).to(DEV)
+            gpu = run_gpu(dev, params, 200, history=hist, cand_cap=200, vocab=V, splits=splits, logit_scale=0.75,
+                          logit_softcap=12.0)
+            compare(gpu, ref, 200, where="V %d stride %d splits %d" % (V, stride, splits))
+            assert gpu["status"] == 0
