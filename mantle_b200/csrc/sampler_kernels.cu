@@ -194,7 +194,7 @@ int choose_splits(const MantleSampleBatch* b) {
     const int cap = std::max(1, std::min(std::min(max_by_k, max_by_work), 64));
     const int target = per_sm * smem_budget().sms;  // one full wave
     if (b->rows >= target) return 1;
-    return std::max(1, std::min(cap, (target + b->rows - 1) / b->rows));
+    return std::max(1, std::min(cap, target / b->rows));  // rounded down: all the CTAs in one wave
 }
 
 void fill_args(KArgs& a, const MantleSampleBatch* b) {
