@@ -43,7 +43,13 @@ struct WideCtl {
     uint32_t kmin, kmax;
     int decided;     // radix search: chosen sub-range
     int found_flag;  //               the predicate turned true inside it
+    // Every thread's partial sums of a pass, one column per thread: a read-add-write of shared
+    // memory per element instead of sixteen predicated adds on registers (and 48 registers less).
+    // A thread sees at most MAX_VOCAB / WIDE_NT = 2048 elements per pass, so 16 bits count them.
+    double col_mass[WIDE_FAN][WIDE_NT];
+    uint16_t col_count[WIDE_FAN][WIDE_NT];
 };
+static_assert(MANTLE_SAMPLE_MAX_VOCAB / WIDE_NT < 65536, "per-thread counts are 16 bits wide");
 
 enum { WIDE_KTH = 0, WIDE_CUT = 1, WIDE_DRAW = 2 };
 
@@ -214,13 +220,13 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
         for (;;) {
             // sub-range j covers keys (hi - (j+1)*width, hi - j*width]; j = 0 holds the largest keys
             const uint32_t span = hi - lo;  // >= 0
-            const uint32_t width = span / WIDE_FAN + 1;
-            double m[WIDE_FAN];
-            unsigned long long c[WIDE_FAN];
+            // a power of two just above span / WIDE_FAN: the sub-range of a key is a shift, not a divide
+            const int wshift = 32 - __clz((int)(span / WIDE_FAN));
+            const uint32_t width = 1u << wshift;
 #pragma unroll
             for (int j = 0; j < WIDE_FAN; j++) {
-                m[j] = 0.0;
-                c[j] = 0;
+                w->col_mass[j][tid] = 0.0;
+                w->col_count[j][tid] = 0;
             }
             for (int e = tid; e < V; e += WIDE_NT) {
                 const float v = value(e);
@@ -229,18 +235,14 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
                 if (key < lo || key > hi) continue;
                 double p;
                 if (!weigh(v, key, e, &p)) continue;
-                const int j = (int)((hi - key) / width);
-#pragma unroll
-                for (int q = 0; q < WIDE_FAN; q++)
-                    if (q == j) {
-                        m[q] = __dadd_rn(m[q], p);
-                        c[q]++;
-                    }
+                const int j = (int)((hi - key) >> wshift);
+                w->col_mass[j][tid] = __dadd_rn(w->col_mass[j][tid], p);
+                w->col_count[j][tid]++;
             }
 #pragma unroll
             for (int j = 0; j < WIDE_FAN; j++) {
-                double d = m[j];
-                unsigned long long n = c[j];
+                double d = w->col_mass[j][tid];
+                unsigned long long n = w->col_count[j][tid];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) {
                     d = __dadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
