@@ -16,7 +16,25 @@
  * greedy test and lowest-index argmax, temperature scaling, the top-k shortlist
  * (value descending, ties by ascending index), fastExp softmax over the shortlist in
  * float32 with double sums, min-p, the top-p cut and the inverse-CDF draw from a
- * host-supplied uniform.  Token ids equal the reference's on the same inputs.
+ * host-supplied uniform.
+ *
+ * What "equal to the reference" means.  For batches whose max_top_k is at most
+ * MANTLE_SAMPLE_MAX_TOP_K every double is the reference's double (same operations, same
+ * order): token ids, shortlists, lengths and probabilities are bit-equal.  Batches with a
+ * larger max_top_k (up to the whole vocabulary) never materialise the shortlist; their sums
+ * are taken in a different association than the reference's shortlist order, so a prefix
+ * sum can differ from the reference's in its last bits (about 1e-16 relative).  There the
+ * token, n_kept and cut can differ from the reference's only when the uniform or top_p lies
+ * that close to a boundary of the cumulative distribution -- far inside the 1e-6 the
+ * sampling contract allows -- token_prob and softmax_sum hold to 1e-5 relative (in practice
+ * 1e-15), and cand_idx / cand_prob are not available.
+ *
+ * NaN logits are outside the contract (the reference's own result depends on where in the row
+ * they sit).  Here a NaN is never admitted to a shortlist; a row with no other value returns
+ * token 0 and raises MANTLE_SAMPLE_STATUS_NAN.
+ *
+ * The library keeps a little per-device state (device attributes, kernel attributes, the
+ * address of the static scratch): it must not be used across a cudaDeviceReset.
  */
 #ifndef MANTLE_CUDA_SAMPLER_H
 #define MANTLE_CUDA_SAMPLER_H
@@ -64,8 +82,9 @@ typedef void* mantleCudaStream_t; /* a cudaStream_t, as in native/softmax.h:11 *
 #define MANTLE_SAMPLE_STATUS_TOPK_RANGE 1  /* a row's top_k exceeded max_top_k          */
 #define MANTLE_SAMPLE_STATUS_EMPTY 2       /* a row ended with an empty shortlist (the  */
                                            /* reference panics there); its token is -1  */
-#define MANTLE_SAMPLE_STATUS_TIMEOUT 4     /* a bounded wait on an asynchronous copy ran */
-                                           /* out; the launch stopped early              */
+#define MANTLE_SAMPLE_STATUS_TIMEOUT 4     /* a bounded wait ran out (only the self-test  */
+                                           /* raises it: no sampling kernel waits)        */
+#define MANTLE_SAMPLE_STATUS_NAN 8         /* a row held nothing but NaN; its token is 0  */
 
 /*
  * One batch of rows.  All pointers are device pointers on the current device.
@@ -85,6 +104,13 @@ typedef void* mantleCudaStream_t; /* a cudaStream_t, as in native/softmax.h:11 *
  *               at most cand_stride entries per row are written
  *   n_kept, cut optional out, [rows]: shortlist length after min-p and nucleus length
  *               after top-p; both 0 on greedy rows
+ *   token_prob, softmax_sum  optional out, [rows] doubles: the probability the sampled token
+ *               carries in the reference's prob[] (after the min-p renormalisation, before any
+ *               top-p cut: sampler.go:176, 205) and the softmax normaliser `sum`
+ *               (sampler.go:165-168); both 0 on greedy rows
+ *   skip        optional, [rows] int32: a row whose entry is not 0 is not sampled (a request of
+ *               a batched decode loop that has already ended); its token is -1, its other
+ *               outputs 0, and nothing of its logits or history is read
  *   status      optional out: one int32 the kernels OR status bits into
  *   max_top_k   an upper bound of min(params[r].top_k, vocab) over the batch; sizes the
  *               workspace.  Above MANTLE_SAMPLE_MAX_TOP_K the whole batch takes the
@@ -124,6 +150,9 @@ typedef struct MantleSampleBatch {
     uint32_t reserved;
     float logit_scale;
     float logit_softcap;
+    double* token_prob;
+    double* softmax_sum;
+    const int32_t* skip;
 } MantleSampleBatch;
 
 /*

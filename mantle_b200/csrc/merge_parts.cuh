@@ -7,8 +7,8 @@ namespace {
 
 // Merge of `parts` local shortlists per row (several CTAs of one GPU, or one per
 // vocabulary shard after an all-gather), then the tail.
-__global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_parts_kernel(const KArgs a) {
-    using S = ShapeLargeK;
+__global__ void __launch_bounds__(ShapeK1024::NT, ShapeK1024::MINB) merge_parts_kernel(const KArgs a) {
+    using S = ShapeK1024;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Cand* buf = reinterpret_cast<Cand*>(smem_raw);
     uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
@@ -16,6 +16,10 @@ __global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_part
     const int tid = threadIdx.x;
     const int row = blockIdx.x;
 
+    if (a.skip && a.skip[row] != 0) {
+        if (tid == 0) publish_row(a, row, -1);
+        return;
+    }
     const MantleSampleParams P = row_params(a, row);
     const bool greedy = P.greedy != 0 || (P.top_k == 1 && P.top_p >= 1.0f && P.temperature == 1.0f);
     int k = greedy ? 1 : min(P.top_k, a.vocab_total);
@@ -63,9 +67,7 @@ __global__ void __launch_bounds__(ShapeLargeK::NT, ShapeLargeK::MINB) merge_part
     if (bad_k) {
         if (tid == 0) {
             if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_TOPK_RANGE);
-            a.next[row] = -1;
-            if (a.n_kept) a.n_kept[row] = 0;
-            if (a.cut) a.cut[row] = 0;
+            publish_row(a, row, -1);
         }
         return;
     }

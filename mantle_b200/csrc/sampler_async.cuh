@@ -1,4 +1,4 @@
-// mbarriers, untiled bulk copies (TMA), cp.async and the bounded waits on them.
+// mbarriers and the bounded wait on them, with its self-test kernel.
 // Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
 // translation unit.
 #pragma once
@@ -6,19 +6,15 @@
 namespace {
 
 // ---------------------------------------------------------------------------------------
-// Asynchronous bulk copies (TMA, untiled form) and the mbarriers that track them.
-// Both addresses are 16-byte aligned and sizes are multiples of 16 bytes by construction:
-// copies move whole 16-byte vectors from the row rounded down to a 16-byte boundary.
+// Waiting on an mbarrier with a limit.  No kernel of the sampler waits on anything another CTA,
+// copy engine or GPU completes -- the streaming kernel uses plain loads -- so the only user is the
+// self-test below, which shows the pattern any future asynchronous stage has to follow: a wait
+// that gives up, reports and returns instead of spinning without bound.
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
 }
 
 constexpr uint32_t WAIT_HINT_NS = 20000;
@@ -71,28 +67,5 @@ __global__ void bounded_wait_selftest_kernel(uint64_t limit_ns, int32_t* status)
     const bool landed = mbar_wait(&bar, 0, limit_ns);
     if (!landed && threadIdx.x == 0) atomicOr(status, MANTLE_SAMPLE_STATUS_TIMEOUT);
 }
-
-__device__ __forceinline__ uint64_t evict_first_policy() {
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
-        : "memory");
-}
-
-// Small asynchronous copies (8 or 4 bytes) for the next item's parameters.
-__device__ __forceinline__ void cp_async8(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 }  // namespace

@@ -29,9 +29,12 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
+#include <cmath>
 #include <mutex>
 
 #include "../../include/mantle_cuda_sampler.h"
+#include "sampler_internal.h"
 
 // Development aid, compiled out of the shipped library: with -DMANTLE_DEBUG_SWITCHES the
 // environment variable MANTLE_SAMPLER_DEBUG switches pieces of the kernel off to cost them.
@@ -46,7 +49,6 @@
 #include "sampler_tail.cuh"
 #include "sampler_async.cuh"
 #include "sampler_rows.cuh"
-#include "scan_rows_ring.cuh"
 #include "scan_rows_ldg.cuh"
 #include "wide_rows.cuh"
 #include "merge_parts.cuh"
@@ -101,98 +103,70 @@ bool batch_ok(const MantleSampleBatch* b, bool need_outputs) {
     return true;
 }
 
-// Shape selection.  MANTLE_SAMPLER_SHAPE=small|large overrides it (a tuning aid: `small`
-// is refused, by falling back, for batches whose top_k it cannot serve).
-int forced_shape() {
-    static const int forced = [] {
-        const char* e = getenv("MANTLE_SAMPLER_SHAPE");
-        if (!e) return 0;
-        return strcmp(e, "small") == 0 ? 1 : (strcmp(e, "large") == 0 ? 2 : (strcmp(e, "alt") == 0 ? 3 : 0));
-    }();
-    return forced;
-}
-
-// MANTLE_SAMPLER_KERNEL=ldg|tma picks the streaming kernel for shortlists of at most 256 entries.
-int forced_kernel() {
-    static const int forced = [] {
-        const char* e = getenv("MANTLE_SAMPLER_KERNEL");
-        if (!e) return 0;
-        return strcmp(e, "ldg") == 0 ? 1 : (strcmp(e, "tma") == 0 ? 2 : 0);
-    }();
-    return forced;
-}
-
-bool use_small_shape(int max_top_k) {
-    if (max_top_k > ShapeSmallK::KCAP) return false;
-    return forced_shape() != 2;
-}
-
-// Which streaming kernel serves a batch: plain loads, unless MANTLE_SAMPLER_KERNEL=tma asks for
-// the bulk-copy ring (which has no post-processing form).  Measured on 151 936-column float32
-// rows, plain loads against the ring: 0.403 against 0.541 ms for 4096 rows at top_k 20;
-// 0.93 against 1.06 ms (top_k 300), 1.22 against 1.46 ms (512), 3.70 against 3.86 ms (1024)
-// for 2048 rows.
-bool use_ldg(int max_top_k, bool post) {
-    (void)max_top_k;
-    return post || forced_kernel() != 2;
-}
-
-bool use_alt_shape(int max_top_k) { return forced_shape() == 3 && max_top_k <= ShapeAlt::KCAP; }
-
-struct SmemBudget {
+// What the library asks a device once and then remembers: the driver calls behind these
+// figures cost microseconds, which shows on a single-row launch of under twenty.
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
     int per_sm;     // shared memory of one SM
     int per_block;  // largest opt-in dynamic shared memory of one CTA
     int sms;
 };
+DeviceInfo g_device_info[kMaxDevices];
+std::atomic<int> g_device_known[kMaxDevices];
+std::mutex g_device_mutex;
 
-SmemBudget smem_budget() {
-    SmemBudget b = {233472, 232448, 148};  // B200 figures, used when no device can be asked
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return b;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess && v > 0) b.per_sm = v;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess && v > 0) b.per_block = v;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) b.sms = v;
-    return b;
-}
-
-// Ring depth and CTAs per SM for one shape and vocabulary: as many stages as fit beside the
-// candidate buffer and the bitmap with MINB CTAs on an SM; one CTA per SM with a deeper ring
-// when fewer than two stages would fit.
-template <class S>
-bool plan_ring(int vocab, const SmemBudget& bud, int* stages, int* ctas_per_sm, size_t* smem) {
-    const size_t chunk = (size_t)S::NT * S::U * 16;
-    const size_t fixed = S::SMEM_FIXED + bitmap_words(vocab) * sizeof(uint32_t);
-    for (int ctas = S::MINB; ctas >= 1; ctas--) {
-        const long long room = std::min<long long>(bud.per_sm / ctas - 1024, bud.per_block) - (long long)fixed;
-        int st = room > 0 ? (int)(room / (long long)chunk) : 0;
-        st = std::min(st, ctas == 1 ? 6 : 3);
-        if (st >= 2) {
-            *stages = st;
-            *ctas_per_sm = ctas;
-            *smem = fixed + (size_t)st * chunk;
-            return true;
-        }
+// Current device ordinal and its figures.  Without a usable device (argument checks run on
+// hosts that have none) the B200's own figures stand in and the ordinal is -1.
+DeviceInfo device_info(int* dev_out = nullptr) {
+    const DeviceInfo b200 = {233472, 232448, 148};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        (void)cudaGetLastError();
+        if (dev_out) *dev_out = -1;
+        return b200;
     }
-    return false;
+    if (dev_out) *dev_out = dev;
+    if (g_device_known[dev].load(std::memory_order_acquire)) return g_device_info[dev];
+    std::lock_guard<std::mutex> lock(g_device_mutex);
+    DeviceInfo d = b200;
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess && v > 0) d.per_sm = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess && v > 0) d.per_block = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) d.sms = v;
+    g_device_info[dev] = d;
+    g_device_known[dev].store(1, std::memory_order_release);
+    return d;
 }
+
+// Raises a kernel's dynamic shared-memory limit on the current device when `smem` exceeds what
+// an earlier launch already asked for; `granted` is the kernel's own per-device record.
+template <class K>
+int ensure_smem(K kern, size_t smem, std::atomic<int>* granted) {
+    int dev = -1;
+    (void)device_info(&dev);
+    if (dev >= 0 && (size_t)granted[dev].load(std::memory_order_relaxed) >= smem) return 0;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0) granted[dev].store((int)smem, std::memory_order_relaxed);
+    return 0;
+}
+
+bool small_shape(int max_top_k) { return max_top_k <= ShapeK256::KCAP; }
 
 int choose_splits(const MantleSampleBatch* b) {
     if (b->max_top_k > KMAX) return 1;  // long shortlists: one CTA per row, no merge
     const int vec = b->dtype == MANTLE_DTYPE_F32 ? 4 : 8;
     const int nvec = (b->vocab + vec - 1) / vec + 1;
-    const bool ldg = use_ldg(b->max_top_k, post_mode_of(b->logit_scale, b->logit_softcap, b->flags) != 0);
-    const bool small = ldg ? b->max_top_k <= ShapeLdg::KCAP : use_small_shape(b->max_top_k);
-    const int chunk = ldg ? (small ? ShapeLdg::NT * ShapeLdg::U : ShapeLdgLargeK::NT * ShapeLdgLargeK::U)
-                          : (small ? ShapeSmallK::NT * ShapeSmallK::U : ShapeLargeK::NT * ShapeLargeK::U);
-    const int per_sm = ldg ? (small ? ShapeLdg::MINB : ShapeLdgLargeK::MINB)
-                           : (small ? ShapeSmallK::MINB : ShapeLargeK::MINB);
+    const bool small = small_shape(b->max_top_k);
+    const int region = small ? ShapeK256::NT * ShapeK256::U : ShapeK1024::NT * ShapeK1024::U;
+    const int per_sm = small ? ShapeK256::MINB : ShapeK1024::MINB;
     const int max_by_k = MERGE_CAP / b->max_top_k;  // the merge holds splits * k candidates
     if (b->splits > 0) return std::max(1, std::min(std::min(b->splits, max_by_k), std::min(nvec, 64)));
     // at least one full region per CTA (measured on one 151 936-column row: 9 CTAs 21.8 us, 18 19.0 us,
     // 37 17.7 us, 64 18.7 us)
-    const int max_by_work = nvec / chunk;
+    const int max_by_work = nvec / region;
     const int cap = std::max(1, std::min(std::min(max_by_k, max_by_work), 64));
-    const int target = per_sm * smem_budget().sms;  // one full wave
+    const int target = per_sm * device_info().sms;  // one full wave
     if (b->rows >= target) return 1;
     return std::max(1, std::min(cap, target / b->rows));  // rounded down: all the CTAs in one wave
 }
@@ -219,6 +193,9 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
     a.n_kept = b->n_kept;
     a.cut = b->cut;
     a.status = b->status;
+    a.token_prob = b->token_prob;
+    a.softmax_sum = b->softmax_sum;
+    a.skip = b->skip;
     a.cand_stride = b->cand_stride;
     a.part_val = nullptr;
     a.part_idx = nullptr;
@@ -227,7 +204,6 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
     a.part_stride = 0;
     a.cnt_stride = 0;
     a.parts = 0;
-    a.hist_tma_ok = a.history && reinterpret_cast<uintptr_t>(a.history) % 16 == 0 && a.hist_stride % 4 == 0;
     a.post.mode = post_mode_of(b->logit_scale, b->logit_softcap, b->flags);
     a.post.scale = b->logit_scale;
     a.post.cap = b->logit_softcap;
@@ -237,91 +213,66 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
 #endif
 }
 
-template <class S, int MODE>
-int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
-    const SmemBudget bud = smem_budget();
-    int stages = 0, ctas = 0;
-    size_t smem = 0;
-    if (!plan_ring<S>(a.vocab, bud, &stages, &ctas, &smem)) return kInvalid;
-    const long long items = (long long)a.rows * a.splits;
-    if (items > 0x7fffffffLL) return kInvalid;
-    const int grid = (int)std::min<long long>(items, (long long)ctas * bud.sms);
-    cudaError_t e;
-    if (dtype == MANTLE_DTYPE_F32) {
-        auto kern = scan_rows_kernel<S, float, MODE>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        kern<<<grid, S::NT, smem, stream>>>(a, stages);
-    } else {
-        auto kern = scan_rows_kernel<S, bf16_t, MODE>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        kern<<<grid, S::NT, smem, stream>>>(a, stages);
-    }
-    return (int)cudaGetLastError();
-}
-
 template <class S, typename T, int MODE, bool POST>
-int launch_scan_ldg_as(const KArgs& a, cudaStream_t stream) {
-    const size_t smem = LdgLayout<S>::FIXED + bitmap_words(a.vocab) * sizeof(uint32_t);
+int launch_scan_as(const KArgs& a, cudaStream_t stream) {
+    static std::atomic<int> granted[kMaxDevices];
+    const size_t smem = S::SMEM_FIXED + bitmap_words(a.vocab) * sizeof(uint32_t);
     const long long items = (long long)a.rows * a.splits;
     if (items > 0x7fffffffLL) return kInvalid;
     auto kern = scan_rows_ldg_kernel<S, T, MODE, POST>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    const int rc = ensure_smem(kern, smem, granted);
+    if (rc) return rc;
     kern<<<(int)items, S::NT, smem, stream>>>(a);
     return (int)cudaGetLastError();
 }
 
 template <class S, int MODE>
-int launch_scan_ldg(const KArgs& a, int dtype, cudaStream_t stream) {
+int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
     if (a.post.mode)
-        return dtype == MANTLE_DTYPE_F32 ? launch_scan_ldg_as<S, float, MODE, true>(a, stream)
-                                         : launch_scan_ldg_as<S, bf16_t, MODE, true>(a, stream);
-    return dtype == MANTLE_DTYPE_F32 ? launch_scan_ldg_as<S, float, MODE, false>(a, stream)
-                                     : launch_scan_ldg_as<S, bf16_t, MODE, false>(a, stream);
+        return dtype == MANTLE_DTYPE_F32 ? launch_scan_as<S, float, MODE, true>(a, stream)
+                                         : launch_scan_as<S, bf16_t, MODE, true>(a, stream);
+    return dtype == MANTLE_DTYPE_F32 ? launch_scan_as<S, float, MODE, false>(a, stream)
+                                     : launch_scan_as<S, bf16_t, MODE, false>(a, stream);
 }
 
+// The streaming kernel in the shape that serves the batch's longest shortlist.
 template <int MODE>
 int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
-    if (use_ldg(a.max_top_k, a.post.mode != 0)) {
-        if (a.max_top_k <= ShapeLdg::KCAP) return launch_scan_ldg<ShapeLdg, MODE>(a, dtype, stream);
-        return launch_scan_ldg<ShapeLdgLargeK, MODE>(a, dtype, stream);
-    }
-    if (use_alt_shape(a.max_top_k)) return launch_scan_shape<ShapeAlt, MODE>(a, dtype, stream);
-    if (use_small_shape(a.max_top_k)) return launch_scan_shape<ShapeSmallK, MODE>(a, dtype, stream);
-    return launch_scan_shape<ShapeLargeK, MODE>(a, dtype, stream);
+    if (small_shape(a.max_top_k)) return launch_scan_shape<ShapeK256, MODE>(a, dtype, stream);
+    return launch_scan_shape<ShapeK1024, MODE>(a, dtype, stream);
 }
 
 int launch_merge(KArgs& a, cudaStream_t stream) {
+    static std::atomic<int> granted[kMaxDevices];
     if (a.part_stride == 0) a.part_stride = (long long)a.rows * a.part_cap;
     if (a.cnt_stride == 0) a.cnt_stride = a.rows;
-    const size_t smem = ShapeLargeK::SMEM_FIXED;
-    cudaError_t e = cudaFuncSetAttribute(merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    merge_parts_kernel<<<a.rows, ShapeLargeK::NT, smem, stream>>>(a);
+    const size_t smem = ShapeK1024::SMEM_FIXED;
+    const int rc = ensure_smem(merge_parts_kernel, smem, granted);
+    if (rc) return rc;
+    merge_parts_kernel<<<a.rows, ShapeK1024::NT, smem, stream>>>(a);
     return (int)cudaGetLastError();
 }
 
 int launch_wide(const KArgs& a, int dtype, cudaStream_t stream) {
+    static std::atomic<int> granted[2][kMaxDevices];
     const size_t smem = ((sizeof(WideCtl) + 127) / 128) * 128 + bitmap_words(a.vocab) * sizeof(uint32_t);
-    cudaError_t e;
     if (dtype == MANTLE_DTYPE_F32) {
-        e = cudaFuncSetAttribute(wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
+        const int rc = ensure_smem(wide_rows_kernel<float>, smem, granted[0]);
+        if (rc) return rc;
         wide_rows_kernel<float><<<a.rows, WIDE_NT, smem, stream>>>(a);
     } else {
-        e = cudaFuncSetAttribute(wide_rows_kernel<bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
+        const int rc = ensure_smem(wide_rows_kernel<bf16_t>, smem, granted[1]);
+        if (rc) return rc;
         wide_rows_kernel<bf16_t><<<a.rows, WIDE_NT, smem, stream>>>(a);
     }
     return (int)cudaGetLastError();
 }
 
 int launch_penalty(const KArgs& a, cudaStream_t stream) {
+    static std::atomic<int> granted[kMaxDevices];
     const size_t smem = bitmap_words(a.vocab) * sizeof(uint32_t);
-    cudaError_t e = cudaFuncSetAttribute(penalty_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    const int rc = ensure_smem(penalty_rows_kernel, smem, granted);
+    if (rc) return rc;
     penalty_rows_kernel<<<a.rows, PENALTY_NT, smem, stream>>>(a);
     return (int)cudaGetLastError();
 }
@@ -343,7 +294,7 @@ size_t parts_bytes(int rows, int parts, int cap) {
 
 }  // namespace
 
-extern "C" int mantleCudaSamplerAbiVersion(void) { return 2; }
+extern "C" int mantleCudaSamplerAbiVersion(void) { return 3; }
 
 extern "C" int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* splits) {
     if (!splits || !batch_ok(batch, true)) return kInvalid;
@@ -402,7 +353,7 @@ extern "C" int mantleCudaLogitPostprocessRowsF32(float* logits, int rows, int vo
     Post post = {post_mode_of(logit_scale, logit_softcap, flags), logit_scale, logit_softcap};
     if (!post.mode) return 0;
     const long long n = (long long)rows * vocab;
-    const int grid = (int)std::min<long long>((n + 255) / 256, (long long)smem_budget().sms * 32);
+    const int grid = (int)std::min<long long>((n + 255) / 256, (long long)device_info().sms * 32);
     postprocess_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_)>>>(logits, rows, vocab, row_stride, post);
     return (int)cudaGetLastError();
 }
@@ -518,7 +469,8 @@ inline size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
 
 // Carves the device workspace for a host batch.  Returns the total size.
 struct HostPlan {
-    size_t logits, history, hist_len, exclude, params, next, cand_idx, cand_prob, n_kept, cut, status, split, total;
+    size_t logits, history, hist_len, exclude, params, next, cand_idx, cand_prob, n_kept, cut, status, token_prob,
+        softmax_sum, skip, split, total;
     size_t logits_bytes, history_bytes, split_bytes;
 };
 
@@ -545,6 +497,9 @@ HostPlan plan_host(const MantleSampleBatch* b) {
     p.n_kept = take(b->n_kept ? rows * 4 : 0);
     p.cut = take(b->cut ? rows * 4 : 0);
     p.status = take(b->status ? 4 : 0);
+    p.token_prob = take(b->token_prob ? rows * 8 : 0);
+    p.softmax_sum = take(b->softmax_sum ? rows * 8 : 0);
+    p.skip = take(b->skip ? rows * 4 : 0);
     const int s = choose_splits(b);
     p.split_bytes = s > 1 ? parts_bytes(b->rows, s, b->max_top_k) : 0;
     p.split = take(p.split_bytes);
@@ -583,6 +538,7 @@ extern "C" int mantleCudaSampleRowsHost(const MantleSampleBatch* hb, void* devic
     if (hb->n_exclude)
         MANTLE_TRY(cudaMemcpyAsync(ws + p.exclude, hb->exclude, (size_t)hb->n_exclude * 4, cudaMemcpyHostToDevice, stream));
     MANTLE_TRY(cudaMemcpyAsync(ws + p.params, hb->params, rows * sizeof(MantleSampleParams), cudaMemcpyHostToDevice, stream));
+    if (hb->skip) MANTLE_TRY(cudaMemcpyAsync(ws + p.skip, hb->skip, rows * 4, cudaMemcpyHostToDevice, stream));
     if (hb->status) MANTLE_TRY(cudaMemsetAsync(ws + p.status, 0, 4, stream));
 
     MantleSampleBatch d = *hb;
@@ -597,6 +553,9 @@ extern "C" int mantleCudaSampleRowsHost(const MantleSampleBatch* hb, void* devic
     d.n_kept = hb->n_kept ? reinterpret_cast<int32_t*>(ws + p.n_kept) : nullptr;
     d.cut = hb->cut ? reinterpret_cast<int32_t*>(ws + p.cut) : nullptr;
     d.status = hb->status ? reinterpret_cast<int32_t*>(ws + p.status) : nullptr;
+    d.token_prob = hb->token_prob ? reinterpret_cast<double*>(ws + p.token_prob) : nullptr;
+    d.softmax_sum = hb->softmax_sum ? reinterpret_cast<double*>(ws + p.softmax_sum) : nullptr;
+    d.skip = hb->skip ? reinterpret_cast<const int32_t*>(ws + p.skip) : nullptr;
     int rc = mantleCudaSampleRows(&d, p.split_bytes ? ws + p.split : nullptr, p.split_bytes, stream_);
     if (rc) return rc;
 
@@ -608,6 +567,10 @@ extern "C" int mantleCudaSampleRowsHost(const MantleSampleBatch* hb, void* devic
     if (hb->n_kept) MANTLE_TRY(cudaMemcpyAsync(hb->n_kept, ws + p.n_kept, rows * 4, cudaMemcpyDeviceToHost, stream));
     if (hb->cut) MANTLE_TRY(cudaMemcpyAsync(hb->cut, ws + p.cut, rows * 4, cudaMemcpyDeviceToHost, stream));
     if (hb->status) MANTLE_TRY(cudaMemcpyAsync(hb->status, ws + p.status, 4, cudaMemcpyDeviceToHost, stream));
+    if (hb->token_prob)
+        MANTLE_TRY(cudaMemcpyAsync(hb->token_prob, ws + p.token_prob, rows * 8, cudaMemcpyDeviceToHost, stream));
+    if (hb->softmax_sum)
+        MANTLE_TRY(cudaMemcpyAsync(hb->softmax_sum, ws + p.softmax_sum, rows * 8, cudaMemcpyDeviceToHost, stream));
     if (hb->flags & MANTLE_SAMPLE_WRITE_BACK_PENALTY)
         MANTLE_TRY(cudaMemcpyAsync(const_cast<void*>(hb->logits), ws + p.logits, p.logits_bytes, cudaMemcpyDeviceToHost, stream));
 #undef MANTLE_TRY
@@ -629,9 +592,8 @@ namespace {
 constexpr size_t kStaticScratchBytes = (size_t)4 << 20;  // 4 MiB
 static __device__ __align__(256) unsigned char g_split_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 void* g_scratch_addr[kMaxDevices];    // device address of g_split_scratch, per device ordinal
-bool g_scratch_known[kMaxDevices];
+std::atomic<int> g_scratch_known[kMaxDevices];
 std::mutex g_scratch_mutex;
 thread_local char g_last_error[256];
 
@@ -650,16 +612,20 @@ int static_scratch(void** out) {
                        (unsigned long long)dev, (unsigned long long)kMaxDevices);
         return kInvalid;
     }
-    std::lock_guard<std::mutex> lock(g_scratch_mutex);
-    if (!g_scratch_known[dev]) {
-        void* p = nullptr;
-        e = cudaGetSymbolAddress(&p, g_split_scratch);
-        if (e != cudaSuccess) {
-            set_last_error("cudaGetSymbolAddress failed with cudaError %llu", (unsigned long long)e);
-            return (int)e;
+    // The address is looked up once per device and lives as long as the device's primary context:
+    // a cudaDeviceReset in this process invalidates it, and the library must not be used across one.
+    if (!g_scratch_known[dev].load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(g_scratch_mutex);
+        if (!g_scratch_known[dev].load(std::memory_order_relaxed)) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_split_scratch);
+            if (e != cudaSuccess) {
+                set_last_error("cudaGetSymbolAddress failed with cudaError %llu", (unsigned long long)e);
+                return (int)e;
+            }
+            g_scratch_addr[dev] = p;
+            g_scratch_known[dev].store(1, std::memory_order_release);
         }
-        g_scratch_addr[dev] = p;
-        g_scratch_known[dev] = true;
     }
     *out = g_scratch_addr[dev];
     return 0;
@@ -668,6 +634,8 @@ int static_scratch(void** out) {
 }  // namespace
 
 extern "C" const char* mantleCudaSamplerLastError(void) { return g_last_error; }
+
+void mantle_internal_set_last_error(const char* msg) { snprintf(g_last_error, sizeof g_last_error, "%s", msg); }
 
 extern "C" size_t mantleCudaSamplerStaticScratchBytes(void) { return kStaticScratchBytes; }
 

@@ -16,18 +16,13 @@ __device__ void sample_tail(const KArgs& a, int row, const MantleSampleParams& P
     constexpr int NT = S::NT;
     if (n == 0) {  // only an all-NaN row ends here; the reference's behaviour there is undefined
         if (tid == 0) {
-            a.next[row] = 0;
-            if (a.n_kept) a.n_kept[row] = 0;
-            if (a.cut) a.cut[row] = 0;
+            publish_row(a, row, 0);
+            if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_NAN);
         }
         return;
     }
     if (greedy) {
-        if (tid == 0) {
-            a.next[row] = sidx[0];
-            if (a.n_kept) a.n_kept[row] = 0;
-            if (a.cut) a.cut[row] = 0;
-        }
+        if (tid == 0) publish_row(a, row, sidx[0]);
         return;
     }
     const float maxv = sval[0];
@@ -41,11 +36,7 @@ __device__ void sample_tail(const KArgs& a, int row, const MantleSampleParams& P
     __syncthreads();
     const double sum = ctl->sum;
     if (sum == 0.0) {  // sampler.go:170-172
-        if (tid == 0) {
-            a.next[row] = sidx[0];
-            if (a.n_kept) a.n_kept[row] = n;
-            if (a.cut) a.cut[row] = 0;
-        }
+        if (tid == 0) publish_row(a, row, sidx[0], n, 0);
         return;
     }
     const double inv = __ddiv_rn(1.0, sum);
@@ -85,6 +76,7 @@ __device__ void sample_tail(const KArgs& a, int row, const MantleSampleParams& P
     if (tid == 0) {
         int token;
         int cut = n;
+        double tprob = 0.0;
         if (n == 0) {  // min_p > 1 dropped everything: the reference indexes topIdx[-1] and panics
             token = -1;
             cut = 0;
@@ -107,10 +99,9 @@ __device__ void sample_tail(const KArgs& a, int row, const MantleSampleParams& P
             }
             if (pos < 0) pos = cut - 1;
             token = sidx[pos];
+            tprob = sprob[pos];
         }
-        a.next[row] = token;
-        if (a.n_kept) a.n_kept[row] = n;
-        if (a.cut) a.cut[row] = cut;
+        publish_row(a, row, token, n, cut, tprob, sum);
     }
     if (a.cand_idx || a.cand_prob) {
         const int m = min(n, a.cand_stride);
@@ -134,8 +125,10 @@ __device__ void sample_tail_warp(const KArgs& a, int row, const MantleSamplePara
                                  const Cand* buf, int32_t* sidx, double* sprob, int lane) {
     const unsigned full = 0xffffffffu;
     int token, n_kept = 0, cut = 0;
+    double tprob = 0.0, sum_out = 0.0;
     if (n == 0) {
         token = 0;
+        if (lane == 0 && a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_NAN);
     } else if (greedy) {
         token = (int)buf[0].idx;
     } else {
@@ -149,6 +142,7 @@ __device__ void sample_tail_warp(const KArgs& a, int row, const MantleSamplePara
         double p1 = lane + 32 < n ? (double)fast_exp(__fsub_rn(key2f(c1.key), maxv)) : 0.0;
         double sum = 0.0;
         for (int i = 0; i < n; i++) sum = __dadd_rn(sum, __shfl_sync(full, i < 32 ? p0 : p1, i & 31));
+        sum_out = sum;
         if (sum == 0.0) {  // sampler.go:170-172
             token = __shfl_sync(full, i0, 0);
             n_kept = n;
@@ -215,6 +209,7 @@ __device__ void sample_tail_warp(const KArgs& a, int row, const MantleSamplePara
                 const unsigned r1 = __ballot_sync(full, lane + 32 < cut && r <= c1v);
                 const int pos = r0 ? __ffs(r0) - 1 : (r1 ? 31 + __ffs(r1) : cut - 1);
                 token = __shfl_sync(full, pos < 32 ? i0 : i1, pos & 31);
+                tprob = __shfl_sync(full, pos < 32 ? p0 : p1, pos & 31);
             }
             if (a.cand_idx || a.cand_prob) {
                 const size_t base = (size_t)row * a.cand_stride;
@@ -229,11 +224,7 @@ __device__ void sample_tail_warp(const KArgs& a, int row, const MantleSamplePara
             }
         }
     }
-    if (lane == 0) {
-        a.next[row] = token;
-        if (a.n_kept) a.n_kept[row] = n_kept;
-        if (a.cut) a.cut[row] = cut;
-    }
+    if (lane == 0) publish_row(a, row, token, n_kept, cut, tprob, sum_out);
 }
 
 // After the select: order the survivors and either finish the row or publish the local
@@ -271,17 +262,6 @@ __device__ void finish_row(const KArgs& a, int row, int split, const MantleSampl
         }
         if (tid == 0) a.part_cnt[(size_t)split * a.rows + row] = m;
     }
-}
-
-__device__ __forceinline__ MantleSampleParams row_params(const KArgs& a, int row) {
-    MantleSampleParams P;
-    if (a.params) {
-        P = a.params[row];
-    } else {  // plain argmax of every row
-        P.temperature = 1.0f; P.top_p = 1.0f; P.min_p = 0.0f; P.repeat_penalty = 1.0f;
-        P.top_k = 1; P.repeat_last_n = 1; P.greedy = 1; P.reserved = 0; P.uniform = 0.0;
-    }
-    return P;
 }
 
 }  // namespace

@@ -6,17 +6,10 @@
 namespace {
 
 // ---------------------------------------------------------------------------------------
-// The same streaming pass with plain 16-byte loads instead of the bulk-copy ring: one CTA per
-// item (row, split), two register sets per thread, each refilled from global memory while the
-// other is filtered, one barrier per region of NT*U vectors.  No shared-memory staging, so the
-// CTA is small (candidate buffer + bitmap) and four of them share an SM; which of the two
-// kernels is faster for a batch is a matter of measurement (see launch_scan).
-
-template <class S>
-struct LdgLayout {
-    // shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [bitmap words]
-    static constexpr size_t FIXED = 8 * (size_t)S::CAP + 4 * 256 + 512;
-};
+// The streaming pass: one CTA per item (row, split), plain 16-byte loads, two register sets per
+// thread, each refilled from global memory while the other is filtered, a barrier every second
+// region of NT*U vectors.  No shared-memory staging, so the CTA is small (candidate buffer +
+// bitmap) and four of them share an SM.
 
 template <class S, typename T, int MODE, bool POST>
 __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KArgs a) {
@@ -26,13 +19,20 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     Cand* buf = reinterpret_cast<Cand*>(smem_raw);
     uint32_t* hist = reinterpret_cast<uint32_t*>(buf + CAP);
     Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
-    uint32_t* bm = reinterpret_cast<uint32_t*>(smem_raw + LdgLayout<S>::FIXED);
+    uint32_t* bm = reinterpret_cast<uint32_t*>(smem_raw + S::SMEM_FIXED);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int item = blockIdx.x;
     const int row = item / a.splits;
     const int split = item - row * a.splits;
 
+    if (a.skip && a.skip[row] != 0) {  // a request that has ended: nothing is read, nothing is drawn
+        if (tid == 0) {
+            if (MODE == MODE_FUSED) publish_row(a, row, -1);
+            else a.part_cnt[(size_t)split * a.rows + row] = 0;
+        }
+        return;
+    }
     const MantleSampleParams P = row_params(a, row);
     bool greedy, bad_k;
     const int k = row_k(a, P, S::KCAP, &greedy, &bad_k);
@@ -69,13 +69,11 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     // `ahead(r)`: ask the L2 for region r (one request per 128-byte line), two regions before its
     // loads are issued, so that those loads find their lines on the way or already there
     auto ahead = [&](int r) {
-#if LDG_PREFETCH
         // a warp's share of a region is U runs of 512 bytes: lane i asks for line i & 3 of run i >> 2
         if (r < nreg && lane < 4 * U) {
             const int v = a0 + r * RV + (lane >> 2) * NT + (tid & ~31) + (lane & 3) * 8;
             if (v < b0) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(vbase + v));
         }
-#endif
     };
     if (!careful && nreg > 0) {
         load(ra, 0);
@@ -86,8 +84,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
 
     // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
     const int hl = history_len(a, row);
-    WinPlan wp = win_plan(a, P, hl);
-    wp.staged = false;
+    const WinPlan wp = win_plan(P, hl);
     if (wp.active) {
         build_penalty_bitmap_early<NT>(a, row, wp, hl, c.V, c.voff, bm, tid);
         c.pen_bitmap = true;
@@ -146,7 +143,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             }
         };
 
-        // -- region 0 seeds the threshold (see scan_rows_kernel) --
+        // -- region 0 seeds the threshold --
         if (nreg > 1) load(rb, 1);
         {
             const int v0 = a0 + tid;
@@ -196,19 +193,19 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
 
         // -- regions 1.. : two register sets, each refilled while the other is filtered --
         // The barrier carries only the vote (the register sets are private), so it need not follow
-        // every region: the threshold is refreshed at most every LDG_VOTE_EVERY regions, at the
+        // every region: the threshold is refreshed at most every VOTE_EVERY regions, at the
         // price of a few more survivors under a threshold that is that much staler.
         int r = 1;
         while (r < nreg && !careful) {
             if (r + 1 < nreg) load(ra, r + 1);
             ahead(r + 3);
             later(rb, r);
-            if (r % LDG_VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
+            if (r % VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
             if (++r >= nreg || careful) break;
             if (r + 1 < nreg) load(rb, r + 1);
             ahead(r + 3);
             later(ra, r);
-            if (r % LDG_VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
+            if (r % VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
             ++r;
         }
     }
@@ -236,7 +233,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         __syncthreads();
     }
 
-    if (careful) {  // the careful path of scan_rows_kernel
+    if (careful) {  // the careful path: steps that always fit the buffer
         __syncthreads();
         if (tid == 0) ctl->cnt = 0;
         __syncthreads();
@@ -276,9 +273,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         if (tid == 0) {
             if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_TOPK_RANGE);
             if (MODE == MODE_FUSED) {
-                a.next[row] = -1;
-                if (a.n_kept) a.n_kept[row] = 0;
-                if (a.cut) a.cut[row] = 0;
+                publish_row(a, row, -1);
             } else {
                 a.part_cnt[(size_t)split * a.rows + row] = 0;
             }

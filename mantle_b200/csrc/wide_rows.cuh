@@ -73,15 +73,17 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
     const int row = blockIdx.x;
     const int V = a.vocab;
 
+    if (a.skip && a.skip[row] != 0) {
+        if (tid == 0) publish_row(a, row, -1);
+        return;
+    }
     const MantleSampleParams P = row_params(a, row);
     bool greedy, bad_k;
     const int k = row_k(a, P, 0x7fffffff, &greedy, &bad_k);  // no cap on this path
     if (bad_k) {
         if (tid == 0) {
             if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_TOPK_RANGE);
-            a.next[row] = -1;
-            if (a.n_kept) a.n_kept[row] = 0;
-            if (a.cut) a.cut[row] = 0;
+            publish_row(a, row, -1);
         }
         return;
     }
@@ -89,10 +91,9 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
     const void* rowp = reinterpret_cast<const T*>(a.logits) + (size_t)row * (size_t)a.row_stride;
 
     const int hl = history_len(a, row);
-    WinPlan wp = win_plan(a, P, hl);
-    wp.staged = false;
+    const WinPlan wp = win_plan(P, hl);
     const bool pen = wp.active;
-    if (pen) build_penalty_bitmap(a, row, wp, hl, nullptr, V, a.vocab_offset, bm, tid, WIDE_NT);
+    if (pen) build_penalty_bitmap(a, row, wp, hl, V, a.vocab_offset, bm, tid, WIDE_NT);
 
     // scaled, penalised value of column e and its key
     const Post& post = a.post;
@@ -175,9 +176,8 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
         csync<WIDE_NT>();
         if (tid == 0) {
             for (int i = 1; i < WIDE_NT / 32; i++) best = min(best, w->red_c[i][0]);
-            a.next[row] = best == 0xffffffffffffffffull ? 0 : (int)best + a.vocab_offset;
-            if (a.n_kept) a.n_kept[row] = 0;
-            if (a.cut) a.cut[row] = 0;
+            publish_row(a, row, best == 0xffffffffffffffffull ? 0 : (int)best + a.vocab_offset);
+            if (best == 0xffffffffffffffffull && a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_NAN);
         }
         return;
     }
@@ -424,11 +424,7 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
     unsigned long long n_kept = w->scalar_c;
     csync<WIDE_NT>();
     if (sum == 0.0) {  // sampler.go:170-172: cannot happen (the maximum contributes fastExp(0) = 1), kept for form
-        if (tid == 0) {
-            a.next[row] = 0;
-            if (a.n_kept) a.n_kept[row] = (int)n_kept;
-            if (a.cut) a.cut[row] = 0;
-        }
+        if (tid == 0) publish_row(a, row, 0, (int)n_kept, 0);
         return;
     }
     inv_sum = __ddiv_rn(1.0, sum);
@@ -457,9 +453,7 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
         n_kept = kept;
         if (kept == 0) {  // min_p > 1 dropped everything: the reference indexes topIdx[-1] and panics
             if (tid == 0) {
-                a.next[row] = -1;
-                if (a.n_kept) a.n_kept[row] = 0;
-                if (a.cut) a.cut[row] = 0;
+                publish_row(a, row, -1);
                 if (a.status) atomicOr(a.status, MANTLE_SAMPLE_STATUS_EMPTY);
             }
             return;
@@ -476,11 +470,7 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
     const WideHit h = search(WIDE_DRAW, 0, P.uniform, P.top_p, nucleus);
     const unsigned long long j = tie_position(h, WIDE_DRAW, 0, P.uniform, P.top_p, nucleus);
     const int col = nth_with_key(h.key, j);
-    if (tid == 0) {
-        a.next[row] = col < 0 ? -1 : col + a.vocab_offset;
-        if (a.n_kept) a.n_kept[row] = (int)n_kept;
-        if (a.cut) a.cut[row] = cut;
-    }
+    if (tid == 0) publish_row(a, row, col < 0 ? -1 : col + a.vocab_offset, (int)n_kept, cut, h.p_each, sum);
 }
 
 }  // namespace

@@ -20,6 +20,7 @@ FLAG_SOFTCAP_TANHF = 4
 STATUS_TOPK_RANGE = 1
 STATUS_EMPTY = 2
 STATUS_TIMEOUT = 4
+STATUS_NAN = 8
 CUDA_ERROR_INVALID_VALUE = 1
 
 # MantleSampleParams, include/mantle_sample_params.h
@@ -68,6 +69,9 @@ class SampleBatch(C.Structure):
         ("reserved", C.c_uint32),
         ("logit_scale", C.c_float),
         ("logit_softcap", C.c_float),
+        ("token_prob", C.c_void_p),
+        ("softmax_sum", C.c_void_p),
+        ("skip", C.c_void_p),
     ]
 
 
@@ -138,6 +142,20 @@ HOST_EXPORTS = {
     ),
 }
 
+# include/mantle_batch_sampler.h
+BATCH_EXPORTS = {
+    "mantleBatchSamplerNew": (C.c_void_p, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]),
+    "mantleBatchSamplerFree": (None, [C.c_void_p]),
+    "mantleBatchSamplerSetRow": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(SamplerConfigC), C.c_void_p, C.c_int, C.c_void_p]),
+    "mantleBatchSamplerEndRow": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "mantleBatchSamplerNeedsUniform": (C.c_int, [C.c_void_p, C.c_int]),
+    "mantleBatchSamplerCanUseDeviceGreedy": (C.c_int, [C.c_void_p, C.c_int]),
+    "mantleBatchSamplerStep": (
+        C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_float, C.c_float, C.c_void_p]),
+    "mantleBatchSamplerResults": (
+        C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.POINTER(C.c_void_p)]),
+}
+
 _lib = None
 
 
@@ -167,11 +185,11 @@ def load():
     if not os.path.exists(path):
         raise RuntimeError("CUDA sampler library missing: %s (run python -m mantle_b200.build)" % path)
     L = C.CDLL(path)
-    for name, (res, args) in list(EXPORTS.items()) + list(HOST_EXPORTS.items()):
+    for name, (res, args) in list(EXPORTS.items()) + list(HOST_EXPORTS.items()) + list(BATCH_EXPORTS.items()):
         f = getattr(L, name)  # AttributeError here means the build is broken: do not hide it
         f.restype = res
         f.argtypes = args
-    if L.mantleCudaSamplerAbiVersion() != 2:
+    if L.mantleCudaSamplerAbiVersion() != 3:
         raise RuntimeError("CUDA sampler library ABI mismatch")
     _lib = L
     return L

@@ -68,7 +68,11 @@ def _stream_ptr(stream):
 
 
 class SampleOutputs:
-    __slots__ = ("next", "cand_idx", "cand_prob", "n_kept", "cut", "status")
+    __slots__ = ("next", "cand_idx", "cand_prob", "n_kept", "cut", "status", "token_prob", "softmax_sum")
+
+    def __init__(self):
+        for name in self.__slots__:
+            setattr(self, name, None)
 
 
 class BatchPlan:
@@ -105,6 +109,8 @@ class BatchPlan:
         out.n_kept = torch.zeros(rows, dtype=torch.int32, device=dev) if want_counts else None
         out.cut = torch.zeros(rows, dtype=torch.int32, device=dev) if want_counts else None
         out.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        out.token_prob = torch.zeros(rows, dtype=torch.float64, device=dev) if want_counts else None
+        out.softmax_sum = torch.zeros(rows, dtype=torch.float64, device=dev) if want_counts else None
         self.out = out
         b = native.SampleBatch()
         b.logits = logits.data_ptr()
@@ -132,6 +138,8 @@ class BatchPlan:
         if want_counts:
             b.n_kept = out.n_kept.data_ptr()
             b.cut = out.cut.data_ptr()
+            b.token_prob = out.token_prob.data_ptr()
+            b.softmax_sum = out.softmax_sum.data_ptr()
         b.status = out.status.data_ptr()
         b.splits = splits
         b.flags = flags
@@ -267,6 +275,8 @@ def merge_parts(params, max_top_k, vocab_total, part_val, part_idx, part_cnt, ca
     out.n_kept = torch.zeros(rows, dtype=torch.int32, device=dev)
     out.cut = torch.zeros(rows, dtype=torch.int32, device=dev)
     out.status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out.token_prob = torch.zeros(rows, dtype=torch.float64, device=dev)
+    out.softmax_sum = torch.zeros(rows, dtype=torch.float64, device=dev)
     b = native.SampleBatch()
     b.rows = rows
     b.vocab = vocab_total
@@ -280,6 +290,8 @@ def merge_parts(params, max_top_k, vocab_total, part_val, part_idx, part_cnt, ca
     b.n_kept = out.n_kept.data_ptr()
     b.cut = out.cut.data_ptr()
     b.status = out.status.data_ptr()
+    b.token_prob = out.token_prob.data_ptr()
+    b.softmax_sum = out.softmax_sum.data_ptr()
     with torch.cuda.device(dev):
         rc = lib.mantleCudaSampleMergeParts(C.byref(b), parts, _ptr(part_val), _ptr(part_idx), _ptr(part_cnt), cap,
                                             _stream_ptr(stream))
@@ -312,6 +324,8 @@ class HostBatchPlan:
         out.n_kept = torch.zeros(rows, dtype=torch.int32).pin_memory()
         out.cut = torch.zeros(rows, dtype=torch.int32).pin_memory()
         out.status = torch.zeros(1, dtype=torch.int32).pin_memory()
+        out.token_prob = torch.zeros(rows, dtype=torch.float64).pin_memory()
+        out.softmax_sum = torch.zeros(rows, dtype=torch.float64).pin_memory()
         self.out = out
         b = native.SampleBatch()
         b.logits = self.logits.data_ptr()
@@ -337,6 +351,8 @@ class HostBatchPlan:
         b.n_kept = out.n_kept.data_ptr()
         b.cut = out.cut.data_ptr()
         b.status = out.status.data_ptr()
+        b.token_prob = out.token_prob.data_ptr()
+        b.softmax_sum = out.softmax_sum.data_ptr()
         b.splits = splits
         b.flags = flags
         self.batch = b
@@ -354,7 +370,8 @@ class HostBatchPlan:
                           + sum(t.numel() * t.element_size() for t in (self.history, self.hist_len, self.exclude)
                                 if t is not None))
         self.d2h_bytes = sum(t.numel() * t.element_size()
-                             for t in (out.next, out.cand_idx, out.cand_prob, out.n_kept, out.cut, out.status)
+                             for t in (out.next, out.cand_idx, out.cand_prob, out.n_kept, out.cut, out.status, out.token_prob,
+                                       out.softmax_sum)
                              if t is not None)
 
     def launch(self, stream=None):
@@ -455,3 +472,101 @@ class Sampler:
                                                     self._draw(), _stream_ptr(None), C.byref(tok))
         native.check(rc, "mantleSamplerSampleDevice")
         return tok.value
+
+
+class BatchSampler:
+    """The decode loop's sampling state for `rows` requests at once (include/mantle_batch_sampler.h):
+    what Generator.RunWithContext keeps per request -- toks, the Sampler, the stop tokens
+    (internal/inference/engine.go:189, 233-300) -- held on the device for the whole batch.
+
+        bs = BatchSampler(rows, vocab, hist_capacity, stop_tokens)
+        bs.set_row(r, SamplerConfig(...), context_tokens)      # a request starts
+        while ...:
+            logits = model(...)                                 # [rows, >= vocab] CUDA tensor
+            next_tokens, ended = bs.step(logits, rngs)          # one uniform per live stochastic row
+
+    `rngs[r]` is any callable returning a float in [0, 1): row r's own generator, drawn from exactly
+    when the reference's Sampler of that request would draw (sampler.go:140-142, 224)."""
+
+    def __init__(self, rows, vocab, hist_capacity, stop_tokens=(), device="cuda:0"):
+        self.lib = native.load()
+        self.device = torch.device(device)
+        self.rows, self.vocab = rows, vocab
+        stop = np.ascontiguousarray(list(stop_tokens), dtype=np.int64)
+        with torch.cuda.device(self.device):
+            self.handle = self.lib.mantleBatchSamplerNew(rows, vocab, hist_capacity,
+                                                         stop.ctypes.data_as(C.c_void_p) if stop.size else None, stop.size)
+        if not self.handle:
+            raise RuntimeError("mantleBatchSamplerNew failed")
+        self._uniforms = np.zeros(rows, dtype=np.float64)
+
+    def close(self):
+        if self.handle:
+            with torch.cuda.device(self.device):
+                self.lib.mantleBatchSamplerFree(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_row(self, row, cfg, context=(), stream=None):
+        """A request starts on `row`: NewSampler(cfg) and toks := copy(context)."""
+        c = native.SamplerConfigC(cfg.seed, cfg.temperature, cfg.top_k, cfg.top_p, cfg.min_p, cfg.repeat_penalty,
+                                  cfg.repeat_last_n)
+        ctx = np.ascontiguousarray(list(context), dtype=np.int64)
+        with torch.cuda.device(self.device):
+            rc = self.lib.mantleBatchSamplerSetRow(self.handle, row, C.byref(c),
+                                                   ctx.ctypes.data_as(C.c_void_p) if ctx.size else None, ctx.size,
+                                                   _stream_ptr(stream))
+        native.check(rc, "mantleBatchSamplerSetRow")
+
+    def end_row(self, row, stream=None):
+        with torch.cuda.device(self.device):
+            native.check(self.lib.mantleBatchSamplerEndRow(self.handle, row, _stream_ptr(stream)), "mantleBatchSamplerEndRow")
+
+    def needs_uniform(self, row):
+        return bool(self.lib.mantleBatchSamplerNeedsUniform(self.handle, row))
+
+    def can_use_device_greedy(self, row):
+        return bool(self.lib.mantleBatchSamplerCanUseDeviceGreedy(self.handle, row))
+
+    def draw(self, rngs):
+        """This step's uniforms: one draw from rngs[r] for every row that consumes one."""
+        u = self._uniforms
+        for r in range(self.rows):
+            u[r] = float(rngs[r]()) if self.needs_uniform(r) else 0.0
+        return u
+
+    def step_async(self, logits, uniforms, stream=None, logit_scale=0.0, logit_softcap=0.0):
+        """Queues one step on `stream`; results() after the stream has been synchronised."""
+        if not logits.is_cuda or logits.dim() != 2 or logits.stride(1) != 1 or logits.shape[0] != self.rows:
+            raise ValueError("logits must be a [rows, >= vocab] CUDA tensor with unit column stride")
+        dtype = {torch.float32: native.DTYPE_F32, torch.bfloat16: native.DTYPE_BF16}[logits.dtype]
+        u = np.ascontiguousarray(uniforms, dtype=np.float64)
+        if u.shape != (self.rows,):
+            raise ValueError("one uniform per row")
+        with torch.cuda.device(self.device):
+            rc = self.lib.mantleBatchSamplerStep(self.handle, _ptr(logits), dtype, logits.stride(0),
+                                                 u.ctypes.data_as(C.c_void_p), logit_scale, logit_softcap,
+                                                 _stream_ptr(stream))
+        native.check(rc, "mantleBatchSamplerStep")
+
+    def results(self):
+        """(next tokens, ended flags, status word) of the last step, as numpy arrays (copies)."""
+        nxt, end, dev = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        status = C.c_int32(0)
+        native.check(self.lib.mantleBatchSamplerResults(self.handle, C.byref(nxt), C.byref(end), C.byref(status),
+                                                        C.byref(dev)), "mantleBatchSamplerResults")
+        n = np.ctypeslib.as_array(C.cast(nxt, C.POINTER(C.c_int32)), shape=(self.rows,)).copy()
+        e = np.ctypeslib.as_array(C.cast(end, C.POINTER(C.c_int32)), shape=(self.rows,)).copy()
+        return n, e, status.value
+
+    def step(self, logits, rngs, **kw):
+        """draw + step_async + synchronise + results: one iteration of the reference's loop for the batch."""
+        self.step_async(logits, self.draw(rngs), **kw)
+        torch.cuda.current_stream(self.device).synchronize()
+        n, e, status = self.results()
+        return n, e

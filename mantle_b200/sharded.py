@@ -10,8 +10,11 @@ GPU; internal/api/engine_provider.go:66-71):
   rank merges them and finishes its rows.  Because the ranges are contiguous and ties go to the
   lower global id, the merge of the local shortlists is exactly the global shortlist.
 
-torch.distributed (NCCL on GPUs, gloo in the CPU tests) carries the all-gather; the gathered
-shortlists land in local memory before any kernel reads them.
+Two carriers for the all-gather: `NcclVocabShardedPlan` goes through the library's own entry point
+(mantleCudaSampleVocabSharded: shortlist kernel, ncclAllGather and merge kernel queued by one C
+call on one stream, the form a non-Python host uses); `VocabShardedPlan` and
+`sample_vocab_sharded` let torch.distributed move the blocks (NCCL on GPUs, gloo in the CPU
+tests).  Either way the gathered shortlists land in local memory before any kernel reads them.
 """
 import torch
 import torch.distributed as dist
@@ -69,12 +72,12 @@ class VocabShardedPlan:
     and the merge kernel; nothing is allocated per step."""
 
     def __init__(self, local_logits, params_dev, max_top_k, vocab_total, history=None, hist_len=None, exclude=None,
-                 cand_cap=0, group=None):
+                 cand_cap=0, group=None, world=None, rank=None):
         from . import native, sampler
 
         self.group = group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group) if world is None else world
+        self.rank = dist.get_rank(group) if rank is None else rank
         self.offset, width = vocab_shard(vocab_total, self.world, self.rank)
         if local_logits.shape[1] != width:
             raise ValueError("rank %d holds %d columns, its share of %d is %d"
@@ -111,6 +114,8 @@ class VocabShardedPlan:
         out.n_kept = torch.zeros(rows, dtype=torch.int32, device=dev)
         out.cut = torch.zeros(rows, dtype=torch.int32, device=dev)
         out.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        out.token_prob = torch.zeros(rows, dtype=torch.float64, device=dev)
+        out.softmax_sum = torch.zeros(rows, dtype=torch.float64, device=dev)
         self.out = out
         m = native.SampleBatch()
         m.rows, m.vocab, m.max_top_k = rows, vocab_total, max_top_k
@@ -118,6 +123,7 @@ class VocabShardedPlan:
         if cand_cap:
             m.cand_idx, m.cand_prob, m.cand_stride = out.cand_idx.data_ptr(), out.cand_prob.data_ptr(), cand_cap
         m.n_kept, m.cut, m.status = out.n_kept.data_ptr(), out.cut.data_ptr(), out.status.data_ptr()
+        m.token_prob, m.softmax_sum = out.token_prob.data_ptr(), out.softmax_sum.data_ptr()
         self.merge = m
         self.C = C
 
@@ -132,6 +138,35 @@ class VocabShardedPlan:
         dist.all_gather_into_tensor(self.gathered, self.block, group=self.group)
         rc = self.lib.mantleCudaSampleMergePacked(C.byref(self.merge), self.world, p(self.gathered), self.k, stream)
         native.check(rc, "mantleCudaSampleMergePacked")
+        return self.out
+
+
+class NcclVocabShardedPlan(VocabShardedPlan):
+    """The same step through mantleCudaSampleVocabSharded: one C call per step queues the local
+    shortlist kernel, ncclAllGather on the given communicator and the merge, all on the caller's
+    stream.  `comm` is an mantle_b200.nccl.Communicator whose ranks are the shards in column order."""
+
+    def __init__(self, comm, local_logits, params_dev, max_top_k, vocab_total, **kw):
+        from . import nccl
+
+        self.comm = comm
+        self.nccl_lib = nccl.load()
+        super().__init__(local_logits, params_dev, max_top_k, vocab_total, world=comm.world_size, rank=comm.rank, **kw)
+        # one descriptor serves both kernels: the shard's logits and width, the merge's outputs
+        b = self.local
+        m = self.merge
+        b.next, b.cand_idx, b.cand_prob, b.cand_stride = m.next, m.cand_idx, m.cand_prob, m.cand_stride
+        b.n_kept, b.cut, b.status, b.token_prob, b.softmax_sum = m.n_kept, m.cut, m.status, m.token_prob, m.softmax_sum
+
+    def step(self):
+        C = self.C
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        nccl_rc = C.c_int(0)
+        rc = self.nccl_lib.mantleCudaSampleVocabSharded(
+            C.byref(self.local), self.offset, self.vocab_total, self.comm.handle, C.c_void_p(self.block.data_ptr()),
+            C.c_void_p(self.gathered.data_ptr()), stream, C.byref(nccl_rc))
+        if rc != 0:
+            raise self.native.CudaError(rc, "mantleCudaSampleVocabSharded (ncclResult %d)" % nccl_rc.value)
         return self.out
 
 

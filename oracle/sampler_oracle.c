@@ -207,9 +207,12 @@ int mantle_oracle_topk_sorted(const float *logits, int V, int k, float inv_temp,
 
 /* Everything after the shortlist: sampler.go:154-233.  top_idx/top_val hold `len`
  * entries; prob has room for `len` doubles.  Writes the post-min-p shortlist length to
- * *n_kept and the nucleus length to *cut (either may be NULL). */
+ * *n_kept, the nucleus length to *cut, the softmax normaliser (`sum`, sampler.go:165-168) to
+ * *sum_out and the probability the returned token carries in prob[] to *token_prob (any of
+ * them may be NULL). */
 int mantle_oracle_tail(int32_t *top_idx, const float *top_val, int len, double *prob,
-                       float top_p, float min_p, double r, int *n_kept, int *cut_out) {
+                       float top_p, float min_p, double r, int *n_kept, int *cut_out,
+                       double *sum_out, double *token_prob) {
     float maxv = top_val[0];
     for (int i = 1; i < len; i++)
         if (top_val[i] > maxv) maxv = top_val[i];
@@ -219,6 +222,8 @@ int mantle_oracle_tail(int32_t *top_idx, const float *top_val, int len, double *
         prob[i] = e;
         sum += e;
     }
+    if (sum_out) *sum_out = sum;
+    if (token_prob) *token_prob = 0;
     if (sum == 0) {
         if (n_kept) *n_kept = len;
         if (cut_out) *cut_out = 0;
@@ -264,8 +269,12 @@ int mantle_oracle_tail(int32_t *top_idx, const float *top_val, int len, double *
     double c = 0;
     for (int i = 0; i < cut; i++) {
         c += prob[i];
-        if (r <= c) return top_idx[i];
+        if (r <= c) {
+            if (token_prob) *token_prob = prob[i];
+            return top_idx[i];
+        }
     }
+    if (token_prob) *token_prob = prob[cut - 1];
     return top_idx[cut - 1];
 }
 
@@ -279,12 +288,14 @@ int mantle_oracle_tail(int32_t *top_idx, const float *top_val, int len, double *
  *   n_kept / cut optional: shortlist length after min-p; nucleus length after top-p
  *   use_sort     0: the reference's insertion loop; 1: the equivalent full ordering;
  *                -1: insertion for k <= ORACLE_SORT_THRESHOLD, the ordering above it
- * Greedy rows write n_kept = cut = 0.  V must be > 0.
+ *   softmax_sum / token_prob   optional: the softmax normaliser and the probability of the
+ *                returned token (after the min-p renormalisation)
+ * Greedy rows write n_kept = cut = 0 and softmax_sum = token_prob = 0.  V must be > 0.
  */
 int mantle_oracle_sample_row(float *logits, int V, const int32_t *recent, int n_recent,
                              const int32_t *exclude, int n_exclude, const MantleSampleParams *p,
                              int32_t *cand_idx, double *cand_prob, int cand_cap, int *n_kept,
-                             int *cut, int use_sort) {
+                             int *cut, int use_sort, double *softmax_sum, double *token_prob) {
     if (p->repeat_penalty > 1.0f && n_recent > 0) {
         uint8_t *mark = (uint8_t *)calloc((size_t)V, 1);
         mantle_oracle_apply_penalty(logits, V, recent, n_recent, exclude, n_exclude,
@@ -293,6 +304,8 @@ int mantle_oracle_sample_row(float *logits, int V, const int32_t *recent, int n_
     }
     if (n_kept) *n_kept = 0;
     if (cut) *cut = 0;
+    if (softmax_sum) *softmax_sum = 0;
+    if (token_prob) *token_prob = 0;
     if (p->greedy || (p->top_k == 1 && p->top_p >= 1 && p->temperature == 1))
         return mantle_oracle_argmax(logits, V);
 
@@ -309,7 +322,8 @@ int mantle_oracle_sample_row(float *logits, int V, const int32_t *recent, int n_
         token = 0;
     } else {
         int nk = 0, ct = 0;
-        token = mantle_oracle_tail(top_idx, top_val, len, prob, p->top_p, p->min_p, p->uniform, &nk, &ct);
+        token = mantle_oracle_tail(top_idx, top_val, len, prob, p->top_p, p->min_p, p->uniform, &nk, &ct,
+                                   softmax_sum, token_prob);
         if (n_kept) *n_kept = nk;
         if (cut) *cut = ct;
         int m = nk < cand_cap ? nk : cand_cap;
@@ -343,6 +357,7 @@ typedef struct {
     int cand_stride;
     int32_t *n_kept, *cut;
     int use_sort;
+    double *softmax_sum, *token_prob;
     atomic_int next_row;
 } oracle_job;
 
@@ -365,7 +380,8 @@ static void oracle_one_row(oracle_job *j, int r) {
         row, j->V, h, hl, j->exclude, j->n_exclude, &j->params[r],
         j->cand_idx ? j->cand_idx + (size_t)r * (size_t)j->cand_stride : NULL,
         j->cand_prob ? j->cand_prob + (size_t)r * (size_t)j->cand_stride : NULL, j->cand_stride,
-        &nk, &ct, j->use_sort);
+        &nk, &ct, j->use_sort, j->softmax_sum ? j->softmax_sum + r : NULL,
+        j->token_prob ? j->token_prob + r : NULL);
     if (j->n_kept) j->n_kept[r] = nk;
     if (j->cut) j->cut[r] = ct;
     free(tmp);
@@ -393,6 +409,7 @@ int mantle_oracle_max_threads(void) {
  * hist_len[row] valid ids (NULL: hist_stride); one exclude list for the batch.
  * dtype 0: float32 logits, patched in place; dtype 1: bfloat16 logits, widened exactly
  * to float32 in a private copy (the input is left untouched).
+ * softmax_sum / token_prob: optional [rows] doubles, see mantle_oracle_sample_row.
  * Returns the number of threads used.
  */
 int mantle_oracle_sample_rows(void *logits, int dtype, int rows, int V, int64_t row_stride,
@@ -400,10 +417,11 @@ int mantle_oracle_sample_rows(void *logits, int dtype, int rows, int V, int64_t 
                               const int32_t *exclude, int n_exclude,
                               const MantleSampleParams *params, int32_t *next,
                               int32_t *cand_idx, double *cand_prob, int cand_stride,
-                              int32_t *n_kept, int32_t *cut, int use_sort, int threads) {
+                              int32_t *n_kept, int32_t *cut, int use_sort, int threads,
+                              double *softmax_sum, double *token_prob) {
     oracle_job j = {logits, dtype, rows, V, row_stride, history, hist_stride, hist_len, exclude,
                     n_exclude, params, next, cand_idx, cand_prob, cand_stride, n_kept, cut,
-                    use_sort, 0};
+                    use_sort, softmax_sum, token_prob, 0};
     if (threads <= 0) threads = mantle_oracle_max_threads();
     if (threads > rows) threads = rows > 0 ? rows : 1;
     if (threads <= 1) {

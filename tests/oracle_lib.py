@@ -76,6 +76,7 @@ def lib():
             C.c_void_p, C.c_void_p,
             C.c_void_p, C.c_void_p, C.c_int,
             C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+            C.c_void_p, C.c_void_p,
         ]
         L.mantle_oracle_max_threads.restype = C.c_int
         _lib = L
@@ -131,7 +132,7 @@ def sample_rows(logits, params, history=None, hist_len=None, exclude=None, cand_
 
     logits: [rows, stride] float32 (patched in place, as the reference does) or uint16
     holding bfloat16 bit patterns (left untouched).  Returns a dict with next, n_kept,
-    cut and, when cand_cap > 0, cand_idx / cand_prob.
+    cut, softmax_sum, token_prob and, when cand_cap > 0, cand_idx / cand_prob.
     """
     assert logits.ndim == 2 and logits.flags.c_contiguous
     rows, stride = logits.shape
@@ -155,6 +156,8 @@ def sample_rows(logits, params, history=None, hist_len=None, exclude=None, cand_
     cut = np.zeros(rows, dtype=np.int32)
     cand_idx = np.full((rows, cand_cap), -1, dtype=np.int32) if cand_cap else None
     cand_prob = np.zeros((rows, cand_cap), dtype=np.float64) if cand_cap else None
+    softmax_sum = np.zeros(rows, dtype=np.float64)
+    token_prob = np.zeros(rows, dtype=np.float64)
     used = lib().mantle_oracle_sample_rows(
         _ptr(logits), dtype, rows, V, stride,
         _ptr(history), hs, _ptr(hist_len),
@@ -162,5 +165,7 @@ def sample_rows(logits, params, history=None, hist_len=None, exclude=None, cand_
         _ptr(params), _ptr(nxt),
         _ptr(cand_idx), _ptr(cand_prob), cand_cap,
         _ptr(n_kept), _ptr(cut), use_sort, threads,
+        _ptr(softmax_sum), _ptr(token_prob),
     )
-    return dict(next=nxt, n_kept=n_kept, cut=cut, cand_idx=cand_idx, cand_prob=cand_prob, threads=used)
+    return dict(next=nxt, n_kept=n_kept, cut=cut, cand_idx=cand_idx, cand_prob=cand_prob, threads=used,
+                softmax_sum=softmax_sum, token_prob=token_prob)

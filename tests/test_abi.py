@@ -24,13 +24,13 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), n
         assert n in native.EXPORTS, "binding missing for " + n
-    assert lib.mantleCudaSamplerAbiVersion() == 2
+    assert lib.mantleCudaSamplerAbiVersion() == 3
 
 
 def test_struct_layout_matches_header():
     assert native.PARAMS_DTYPE.itemsize == 40
     assert native.PARAMS_DTYPE.fields["uniform"][1] == 32
-    assert C.sizeof(native.SampleBatch) == 144
+    assert C.sizeof(native.SampleBatch) == 168
     assert native.SampleBatch.row_stride.offset == 24
     assert native.SampleBatch.cand_stride.offset == 120
 
@@ -116,3 +116,40 @@ def test_constructor_normalisation_matches_the_oracle():
         b = O.normalize(uniform=0.25, **cfg)
         assert a.tobytes() == np.array(b).tobytes(), cfg
         assert sampler.can_use_device_greedy(a) == O.can_use_device_greedy(b)
+
+
+def test_batch_sampler_argument_checks_need_no_gpu():
+    """mantleBatchSampler*: bad arguments are refused before any device call."""
+    lib = native.load()
+    inv = native.CUDA_ERROR_INVALID_VALUE
+    assert not lib.mantleBatchSamplerNew(0, 1000, 64, None, 0)
+    assert not lib.mantleBatchSamplerNew(4, 0, 64, None, 0)
+    assert not lib.mantleBatchSamplerNew(4, native.MAX_VOCAB + 1, 64, None, 0)
+    assert not lib.mantleBatchSamplerNew(4, 1000, 1, None, 0)
+    assert not lib.mantleBatchSamplerNew(4, 1000, 64, None, 2)  # two stop tokens, no list
+    cfg = native.SamplerConfigC(0, 1.0, 40, 0.9, 0.0, 1.1, 64)
+    assert lib.mantleBatchSamplerSetRow(None, 0, C.byref(cfg), None, 0, None) == inv
+    assert lib.mantleBatchSamplerEndRow(None, 0, None) == inv
+    assert lib.mantleBatchSamplerStep(None, None, 0, 0, None, 0.0, 0.0, None) == inv
+    assert lib.mantleBatchSamplerResults(None, None, None, None, None) == inv
+    assert lib.mantleBatchSamplerNeedsUniform(None, 0) == 0
+    assert lib.mantleBatchSamplerCanUseDeviceGreedy(None, 0) == 0
+    lib.mantleBatchSamplerFree(None)  # a no-op
+
+
+def test_nccl_entry_point_is_exported_and_checks_its_arguments():
+    """libmantle_cuda_sampler_nccl loads, exports what its header declares and refuses a call
+    without a communicator before touching NCCL or the device."""
+    from mantle_b200 import nccl
+
+    text = open(os.path.join(ROOT, "include", "mantle_cuda_sampler_nccl.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\bint\s+(mantleCuda\w+)\s*\(", text)
+    assert names == ["mantleCudaSampleVocabSharded"]
+    lib = nccl.load()
+    for n in names:
+        assert hasattr(lib, n)
+    rc = C.c_int(-1)
+    b = good_batch()
+    assert lib.mantleCudaSampleVocabSharded(C.byref(b), 0, 1000, None, 0x1000, 0x2000, None, C.byref(rc)) == native.CUDA_ERROR_INVALID_VALUE
+    assert rc.value == 0

@@ -43,6 +43,23 @@ def _rank_main(rank, world, port, tmp):
             gpu2 = dict(next=o2.next.cpu().numpy(), n_kept=o2.n_kept.cpu().numpy(), cut=o2.cut.cpu().numpy(),
                         cand_idx=o2.cand_idx.cpu().numpy(), cand_prob=o2.cand_prob.cpu().numpy())
             compare(gpu2, ref, 50, where="packed, rank %d" % rank)
+        # the same step through the library's own entry point: shortlist kernel, ncclAllGather on a
+        # communicator made with ncclCommInitRank, and merge, queued by one C call
+        from mantle_b200 import nccl
+
+        comm = nccl.communicator_from_torch()
+        plan3 = sharded.NcclVocabShardedPlan(comm, local, p_dev, w.max_top_k, V, history=w.history.to(dev), cand_cap=50)
+        for _ in range(2):
+            o3 = plan3.step()
+            torch.cuda.synchronize()
+            gpu3 = dict(next=o3.next.cpu().numpy(), n_kept=o3.n_kept.cpu().numpy(), cut=o3.cut.cpu().numpy(),
+                        cand_idx=o3.cand_idx.cpu().numpy(), cand_prob=o3.cand_prob.cpu().numpy(),
+                        token_prob=o3.token_prob.cpu().numpy(), softmax_sum=o3.softmax_sum.cpu().numpy())
+            compare(gpu3, ref, 50, where="C entry point, rank %d" % rank)
+            assert int(o3.status.item()) == 0
+        torch.cuda.synchronize()
+        dist.barrier()
+        comm.close()
         open(os.path.join(tmp, "ok%d" % rank), "w").write("ok")
     finally:
         dist.destroy_process_group()

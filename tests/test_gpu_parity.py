@@ -387,7 +387,9 @@ def wide_check(logits_np, params, history=None, exclude=None, bf16=False, where=
     max_k = int(max(params["top_k"].max(), 1025))
     gpu = run_gpu(dev, params, max_k, history, None, exclude, 0)
     ref = O.sample_rows(logits_np.copy(), params, history=history, exclude=exclude, cand_cap=0)
-    compare(gpu, ref, 0, where=where)
+    # sums in a different association than the reference's: the sampled token's probability and the
+    # normaliser are held to the contract's 1e-5 relative, integers to equality
+    compare(gpu, ref, 0, exact_prob=False, where=where)
     assert gpu["status"] == 0
     return gpu, ref
 
