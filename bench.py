@@ -11,11 +11,17 @@ N GPUs every rank samples its own 4096 rows and there is no collective in the da
 
 Prints ONE JSON line on rank 0.  `value` is timed with the batch resident in HBM;
 `e2e` is the same metric through the host-buffer C-ABI call (pinned host inputs, copies
-inside the timed region); `roofline` relates the streaming kernel to measured HBM
-bandwidth; `cpu_baseline` is the CPU port of the reference sampler timed on this host.
+inside the timed region) with the bare link rate beside it; `e2e_device_resident` is a step
+of the batched decode loop (logits already on the device, one parameter record per row up,
+one token per row back); `roofline` relates the streaming kernel to measured HBM bandwidth;
+`cpu_baseline` is the CPU port of the reference sampler timed on this host.
+
+Under torchrun (N > 1) the same line also carries `strong` -- the one 4096-row batch split
+4096/N rows per GPU -- and `vocab_sharded` -- 1024 rows x 262 144 columns split by columns over
+the N GPUs, local shortlist, one NCCL all-gather, merge -- each timed like the headline.
 
 `--impl reference` times that CPU port alone, with every host thread, on the same
-workload (a bounded sample of rows per step) and prints the same kind of line.
+workload and step size, and prints the same kind of line.
 """
 import argparse
 import json
@@ -44,12 +50,26 @@ WORKLOAD_NOTES = {
     "full_vocab_nucleus": "temp 1.0 top_k = vocabulary top_p 0.9 no penalty, seeded N(0,2^2) logits rounded to bf16",
 }
 
-# DRAM bytes one launch of the streaming kernel moves per algorithmic byte, from the ncu
-# capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the
-# algorithmic bytes of the captured launch): profiles/scan_rows_ldg_kernel_2368rows_full.md,
-# 1.4509 GB read + 0.0061 GB written for 1.4488 GB of rows.  Traffic grows with the rows
-# processed, so a full launch is this ratio times its algorithmic bytes.
-DRAM_TRAFFIC_RATIO = 1.006
+
+
+def dram_traffic_ratio(kernel):
+    """DRAM bytes a launch of `kernel` moves per algorithmic byte, from the recorded ncu capture
+    of that kernel (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the
+    captured launch).  Traffic grows with the rows processed, so a full launch is this ratio
+    times its algorithmic bytes.  None when no capture of the kernel is on record."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            rec = json.load(f)[kernel]
+        return (rec["dram_read_bytes"] + rec["dram_write_bytes"]) / rec["algorithmic_bytes"]
+    except Exception:
+        return None
+
+
+def workload_string(name, w):
+    """The one description of a workload both arms print."""
+    return "%s: %d rows x %d %s columns per GPU, history %d ids, %s" % (
+        name, w.rows, w.vocab, "bf16" if w.logits.dtype == torch.bfloat16 else "f32",
+        0 if w.history is None else w.history.shape[1], WORKLOAD_NOTES.get(name, ""))
 
 
 def load_oracle():
@@ -223,15 +243,10 @@ def run_reference(args):
 
     O = load_oracle()
     cores = O.lib().mantle_oracle_max_threads()
-    w = workloads.make(args.workload, rows=min(args.rows, 2048), device="cpu")
+    w = workloads.make(args.workload, rows=args.rows, device="cpu")
     logits = w.logits.numpy()
     hist = None if w.history is None else w.history.numpy()
-    # size a step at roughly one second of wall time
-    n_cal = min(w.rows, max(cores, 16))
-    t = time.perf_counter()
-    O.sample_rows(logits[:n_cal].copy(), w.params[:n_cal], history=None if hist is None else hist[:n_cal])
-    dt = time.perf_counter() - t
-    n = int(min(w.rows, max(n_cal, n_cal * 1.0 / max(dt, 1e-6))))
+    n = w.rows  # a step is the whole batch, as on the GPU arm
     times = []
     used = cores
     for i in range(args.warmup + args.steps):
@@ -248,10 +263,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "%s: %d rows x %d f32 columns per step (bounded sample of the 4096-row batch), "
-                               "history %d ids, temp 0.6 top_k 20 top_p 0.95 repeat_penalty 1.1"
-                               % (args.workload, n, w.vocab, 0 if hist is None else hist.shape[1]),
-                   "rows_per_step": n, "vocab": w.vocab},
+        "config": {"workload": workload_string(args.workload, w), "rows_per_gpu": n, "vocab": w.vocab},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": "port",
                          "sample": "%d rows per step, %d steps" % (n, args.steps)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -259,6 +271,159 @@ def run_reference(args):
         "note": "C port of the reference's Go sampler (no Go toolchain on this image), all host threads",
     }
     print(json.dumps(line), flush=True)
+
+
+def time_link(host_tensor, dev_tensor, world, device, copies=3):
+    """GB/s of a bare pinned host-to-device cudaMemcpyAsync of the e2e leg's logits on this
+    rank's stream (what the link and the host side deliver with nothing else in the way):
+    (this rank, the slowest rank)."""
+    def copy():
+        dev_tensor.copy_(host_tensor, non_blocking=True)
+
+    copy()
+    torch.cuda.synchronize(device)
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    start.record()
+    for _ in range(copies):
+        copy()
+    end.record()
+    torch.cuda.synchronize(device)
+    ms = start.elapsed_time(end) / copies
+    nbytes = host_tensor.numel() * host_tensor.element_size()
+    mine = nbytes / (ms / 1e3) / 1e9
+    slowest = nbytes / (max_over_ranks(ms, world, device) / 1e3) / 1e9
+    return mine, slowest
+
+
+def device_resident_leg(sampler, w, tokens, steps, world, device, clocks):
+    """A step of the batched decode loop through MantleBatchSampler: the logits are where the LM
+    head left them, on the device; per step one parameter record per row goes up (it carries the
+    row's uniform draw) and one token and one flag per row come back.  Histories live on the
+    device and grow by a token per step."""
+    H = 0 if w.history is None else w.history.shape[1]
+    bs = sampler.BatchSampler(w.rows, w.vocab, 2 * max(H, int(w.params["repeat_last_n"].max()), 32), (), device=device)
+    hist = None if w.history is None else w.history.cpu().numpy()
+    for r in range(w.rows):
+        p = w.params[r]
+        cfg = sampler.SamplerConfig(temperature=0.0 if p["greedy"] else float(p["temperature"]), top_k=int(p["top_k"]),
+                                    top_p=float(p["top_p"]), min_p=float(p["min_p"]),
+                                    repeat_penalty=float(p["repeat_penalty"]), repeat_last_n=int(p["repeat_last_n"]))
+        bs.set_row(r, cfg, () if hist is None else hist[r])
+    uniforms = np.ascontiguousarray(w.params["uniform"], dtype=np.float64)
+    stream = torch.cuda.current_stream(device)
+
+    def step():
+        bs.step_async(w.logits, uniforms)
+        stream.synchronize()  # the caller reads the tokens after every step
+
+    step()
+    first, _, status = bs.results()
+    # same logits, histories, parameters and uniforms as the headline launch: same tokens
+    assert np.array_equal(first, tokens) and status == 0, "the batched decode step disagrees with mantleCudaSampleRows"
+    for _ in range(2):
+        step()
+    n = max(3, min(steps, 10))
+    ms = time_steps(step, n, world, device, clocks)
+    bs.close()
+    return {
+        "value": w.rows * world / (ms / 1e3), "unit": UNIT, "ms_per_step": ms, "steps": n,
+        "h2d_bytes_per_step": int(w.rows * 40), "d2h_bytes_per_step": int(w.rows * 8 + 4),
+        "api": "mantleBatchSamplerStep: device logits, parameter records up, tokens and flags down",
+    }
+
+
+def strong_leg(sampler, w, p_dev, ms_full, steps, world, device):
+    """The stated sweep of the throughput configuration: ONE batch of `w.rows` rows split
+    rows / N per GPU (each rank times its share), against this run's own full-batch time."""
+    n = w.rows // world
+    plan = sampler.BatchPlan(w.logits[:n], p_dev[: n * 40], w.max_top_k,
+                             history=None if w.history is None else w.history[:n], want_counts=False)
+    for _ in range(3):
+        plan.launch()
+    ms = time_steps(plan.launch, steps, world, device)
+    return {
+        "rows_total": n * world, "rows_per_gpu": n, "ms_per_step": ms, "value": n * world / (ms / 1e3), "unit": UNIT,
+        "ctas_per_row": plan.splits, "efficiency_vs_n1": (ms_full / world) / ms,
+        "note": "efficiency = (this run's time for the whole batch on one GPU / N) / time for rows/N per GPU; "
+                "the share of a GPU (%.0f MB) %s" % (n * w.bytes_per_row / 1e6,
+                                                      "exceeds the L2" if n * w.bytes_per_row > 2 * 126e6 else "is L2-sized"),
+    }
+
+
+def time_events(fn, steps, device):
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize(device)
+    return start.elapsed_time(end) / steps
+
+
+def vocab_sharded_leg(args, world, rank, device, with_parts=True):
+    """The vocabulary-sharded configuration: 1024 rows x 262 144 columns split evenly over the
+    ranks; a step is mantleCudaSampleVocabSharded -- local shortlist kernel, ncclAllGather of the
+    packed shortlists, merge kernel -- queued by one C call per rank."""
+    import ctypes as C
+
+    import torch.distributed as dist
+
+    from mantle_b200 import nccl, sampler, sharded, workloads
+
+    rows = 1024
+    V = workloads.SPECS["vocab_sharded"]["vocab"]
+    off, width = sharded.vocab_shard(V, world, rank)
+    # every rank generates its own columns on the device from a seed of its own; history and
+    # parameters come from one seed and are identical everywhere
+    w = workloads.make("vocab_sharded", rows=rows, device=device, vocab=width, seed=workloads.BASE_SEED + 4000 + rank)
+    ref = workloads.make("vocab_sharded", rows=rows, device="cpu", vocab=64, seed=workloads.BASE_SEED + 4000)
+    hist = torch.randint(0, V, (rows, 512), generator=torch.Generator().manual_seed(7), dtype=torch.int32).to(device)
+    p_dev = sampler.params_to_device(ref.params, device)
+    comm = nccl.communicator_from_torch()
+    plan = sharded.NcclVocabShardedPlan(comm, w.logits, p_dev, w.max_top_k, V, history=hist)
+    for _ in range(max(args.warmup, 3)):
+        plan.step()
+    ms = time_steps(plan.step, args.steps, world, device)
+    out = {
+        "rows": rows, "vocab_total": V, "columns_per_gpu": width, "ms_per_step": ms, "value": rows / (ms / 1e3),
+        "unit": UNIT, "scaling": "strong", "api": "mantleCudaSampleVocabSharded (one C call per rank and step)",
+        "scan_gbs_per_gpu": None,
+    }
+    if with_parts:
+        # the three pieces on their own, each in a loop of its own (so their sum need not be the step)
+        lib, stream = plan.lib, C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: C.c_void_p(t.data_ptr())
+        scan = lambda: lib.mantleCudaSampleLocalTopK(C.byref(plan.local), plan.offset, V, p(plan.val), p(plan.idx),
+                                                      p(plan.cnt), plan.k, stream)
+        gather = lambda: dist.all_gather_into_tensor(plan.gathered, plan.block)
+        merge = lambda: lib.mantleCudaSampleMergePacked(C.byref(plan.merge), world, p(plan.gathered), plan.k, stream)
+        parts = {}
+        for name, fn in (("scan_us", scan), ("allgather_us", gather), ("merge_us", merge)):
+            for _ in range(3):
+                fn()
+            barrier(world)
+            parts[name] = 1e3 * max_over_ranks(time_events(fn, args.steps, device), world, device)
+        out.update(parts)
+        out["scan_gbs_per_gpu"] = rows * (width * 4 + 4 * 512) / (parts["scan_us"] / 1e6) / 1e9
+    # parity, outside the timed regions: the first 64 rows against the oracle on the whole row
+    n_chk = 64
+    shards = [torch.empty((n_chk, width), dtype=torch.float32, device=device) for _ in range(world)]
+    dist.all_gather(shards, w.logits[:n_chk].contiguous())
+    got = plan.out.next[:n_chk].cpu().numpy()
+    if rank == 0:
+        O = load_oracle()
+        full = torch.cat(shards, dim=1).cpu().numpy()
+        want = O.sample_rows(full, ref.params[:n_chk], history=hist[:n_chk].cpu().numpy())["next"]
+        assert np.array_equal(got, want), "vocabulary-sharded tokens differ from the CPU port on the whole row"
+        out["parity_rows_checked"] = n_chk
+    torch.cuda.synchronize(device)
+    barrier(world)
+    comm.close()
+    return out
 
 
 def run_ours(args):
@@ -294,6 +459,7 @@ def run_ours(args):
 
     # ---- end to end: pinned host buffers through the host-buffer C-ABI call -------------------
     e2e = None
+    resident = None
     if not args.no_e2e:
         host_logits = torch.empty(w.logits.shape, dtype=w.logits.dtype, pin_memory=True)
         host_logits.copy_(w.logits)
@@ -313,14 +479,32 @@ def run_ours(args):
         e2e_steps = max(3, min(args.steps, 10))
         e2e_ms = time_steps(e2e_step, e2e_steps, world, device, clocks)
         assert np.array_equal(hplan.out.next.numpy(), tokens), "host-buffer path disagrees with the device path"
+        h2d_bytes, d2h_bytes = int(hplan.h2d_bytes), int(hplan.d2h_bytes)
+        del hplan
+        # what the link alone delivers for the same bytes, right beside the number it explains
+        scratch = torch.empty_like(w.logits)
+        link_mine, link_slowest = time_link(host_logits, scratch, world, device)
+        del scratch
+        h2d = host_logits.numel() * host_logits.element_size()
         e2e = {
             "value": w.rows * world / (e2e_ms / 1e3), "unit": UNIT, "ms_per_step": e2e_ms, "steps": e2e_steps,
-            "h2d_bytes_per_step": int(hplan.h2d_bytes), "d2h_bytes_per_step": int(hplan.d2h_bytes),
+            "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+            "link_gbs": link_mine, "link_gbs_slowest_rank": link_slowest,
+            "frac_of_link": (h2d / (e2e_ms / 1e3) / 1e9) / link_slowest,
+            "api": "mantleCudaSampleRowsHost: pinned host logits, histories and parameters in, tokens out",
         }
-        del hplan, host_logits
+        del host_logits
+    if not args.no_e2e and w.max_top_k <= native.MAX_TOP_K:
+        resident = device_resident_leg(sampler, w, tokens, args.steps, world, device, clocks)
 
     clocks.stop_flag = True
     clocks.join(timeout=2)
+
+    # ---- the two multi-GPU configurations that are not the headline ---------------------------------
+    strong = sharded_rec = None
+    if world > 1 and args.workload == "throughput" and not post:
+        strong = strong_leg(sampler, w, p_dev, ms, args.steps, world, device)
+        sharded_rec = vocab_sharded_leg(args, world, rank, device)
 
     # ---- CPU baseline and a parity spot check (rank 0, one GPU only) --------------------------------
     cpu = None
@@ -336,14 +520,14 @@ def run_ours(args):
         rows_total = w.rows * world
         kernel_bytes = w.rows * w.bytes_per_row  # one launch, one GPU
         achieved = kernel_bytes / (ms / 1e3) / 1e9
+        kernel = plan.kernel_name
+        ratio = dram_traffic_ratio(kernel) if args.workload == "throughput" and not post else None
         line = {
             "metric": METRIC, "value": rows_total / (ms / 1e3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
-                "workload": "%s: %d rows x %d %s columns per GPU, history %d ids, %s"
-                            % (args.workload, w.rows, w.vocab, "bf16" if w.logits.dtype == torch.bfloat16 else "f32",
-                               0 if w.history is None else w.history.shape[1], WORKLOAD_NOTES.get(args.workload, "")),
+                "workload": workload_string(args.workload, w),
                 "rows_per_gpu": w.rows, "vocab": w.vocab, "parallelism": "rows sharded over %d GPU(s), no collective" % world,
                 "l2": ("inputs (%.2f GB per GPU) exceed the 126 MB L2, no flush needed" % (kernel_bytes / 1e9))
                       if kernel_bytes > 2 * 126e6 else
@@ -353,18 +537,24 @@ def run_ours(args):
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": DRAM_TRAFFIC_RATIO * kernel_bytes if args.workload == "throughput" else None,
+                "traffic": None if ratio is None else ratio * kernel_bytes,
+                "traffic_source": None if ratio is None else "ncu capture of a smaller launch, scaled by rows",
                 "peak_kind": "of %s" % peak_kind, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                "kernel": "wide_rows_kernel" if w.max_top_k > 1024 else "scan_rows_ldg_kernel", "algorithmic_bytes_per_launch": kernel_bytes,
+                "kernel": kernel, "algorithmic_bytes_per_launch": kernel_bytes,
                 "bytes_per_row": w.bytes_per_row,
             },
             "cpu_baseline": cpu,
             "e2e": e2e,
+            "e2e_device_resident": resident,
             "gpu_launches": args.steps * plan.kernels_per_launch,
             "clocks": clocks.summary(),
             "status_word": status,
             "parity_rows_checked": parity_rows,
         }
+        if strong is not None:
+            line["strong"] = strong
+            line["vocab_sharded"] = sharded_rec
+            line["vocab_sharded_parity_rows"] = sharded_rec.get("parity_rows_checked", 0)
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
@@ -373,50 +563,34 @@ def run_ours(args):
 
 
 def run_vocab_sharded(args, world, rank, device):
-    """The vocabulary-sharded configuration: 1024 rows x 262 144 columns split evenly over the
-    ranks; a step is local top-k, one all-gather of the shortlists over NCCL, merge and draw."""
-    from mantle_b200 import sampler, sharded, workloads
+    """`--workload vocab_sharded`: the vocabulary-sharded configuration as a line of its own."""
+    import torch.distributed as dist
 
     if world == 1:
-        import torch.distributed as dist
-
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29533")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
-    rows = min(args.rows, 1024)
-    V = workloads.SPECS["vocab_sharded"]["vocab"]
-    off, width = sharded.vocab_shard(V, world, rank)
-    # every rank generates its own columns on the device from a seed of its own; history and
-    # parameters come from one seed and are identical everywhere
-    w = workloads.make("vocab_sharded", rows=rows, device=device, vocab=width, seed=workloads.BASE_SEED + 4000 + rank)
-    ref = workloads.make("vocab_sharded", rows=rows, device="cpu", vocab=64, seed=workloads.BASE_SEED + 4000)
-    hist = torch.randint(0, V, (rows, 512), generator=torch.Generator().manual_seed(7), dtype=torch.int32).to(device)
-    p_dev = sampler.params_to_device(ref.params, device)
-
-    plan = sharded.VocabShardedPlan(w.logits, p_dev, w.max_top_k, V, history=hist)
-    step = plan.step
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    ms = time_steps(step, args.steps, world, device)
+    rec = vocab_sharded_leg(args, world, rank, device)
     if rank == 0:
         peak, peak_kind = measured_peak()
-        scan_bytes = rows * (width * 4 + 4 * 512)
         line = {
-            "metric": METRIC.replace("151936", "262144 (vocabulary-sharded)"), "value": rows / (ms / 1e3), "unit": UNIT,
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "metric": METRIC.replace("151936", "262144 (vocabulary-sharded)"), "value": rec["value"], "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": rec["ms_per_step"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "vocab_sharded: %d rows x 262144 f32 columns over %d GPU(s) (%d columns each), "
                                    "top_k 50 top_p 0.95 temp 0.7 repeat_penalty 1.15, history 512 ids; local top-k, "
-                                   "one NCCL all-gather of the packed shortlists, merge" % (rows, world, width),
-                       "l2": "per-GPU inputs of %.0f MB; L2-resident below 126 MB" % (scan_bytes / 1e6)},
-            "roofline": {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
-                         "note": "latency-bound: two launches and one collective per step"},
+                                   "one NCCL all-gather of the packed shortlists, merge"
+                                   % (rec["rows"], world, rec["columns_per_gpu"]),
+                       "l2": "per-GPU inputs of %.0f MB; L2-resident below 126 MB"
+                             % (rec["rows"] * (rec["columns_per_gpu"] * 4 + 2048) / 1e6)},
+            "roofline": {"bound": "hbm", "achieved": rec.get("scan_gbs_per_gpu"), "peak": peak, "unit": "GB/s",
+                         "frac": None if not rec.get("scan_gbs_per_gpu") else rec["scan_gbs_per_gpu"] / peak,
+                         "traffic": None, "peak_kind": "of %s" % peak_kind,
+                         "note": "the local shortlist kernel alone; the step is latency-bound: two launches and one collective"},
+            "vocab_sharded": rec,
             "gpu_launches": args.steps * 2,
         }
         print(json.dumps(line), flush=True)
-    import torch.distributed as dist
-
     dist.destroy_process_group()
 
 

@@ -169,6 +169,10 @@ int mantleCudaSamplerWorkspaceBytes(const MantleSampleBatch* batch, size_t* byte
 /* The number of CTAs per row mantleCudaSampleRows will use for this batch. */
 int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* splits);
 
+/* Name of the kernel that reads this batch's logits (for profiles and benchmark records; ""
+ * for a descriptor mantleCudaSampleRows would refuse).  No counterpart in the reference. */
+const char* mantleCudaSamplerKernelName(const MantleSampleBatch* batch);
+
 /*
  * The repeat penalty alone, in place, one scatter over the de-duplicated history
  * window of each row (sampler.go:99-138).  Takes the same descriptor; reads logits

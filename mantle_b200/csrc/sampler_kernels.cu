@@ -302,6 +302,11 @@ extern "C" int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* spli
     return 0;
 }
 
+extern "C" const char* mantleCudaSamplerKernelName(const MantleSampleBatch* batch) {
+    if (!batch_ok(batch, true)) return "";
+    return batch->max_top_k > KMAX ? "wide_rows_kernel" : "scan_rows_ldg_kernel";
+}
+
 extern "C" int mantleCudaSamplerWorkspaceBytes(const MantleSampleBatch* batch, size_t* bytes) {
     if (!bytes || !batch_ok(batch, true)) return kInvalid;
     const int s = choose_splits(batch);

@@ -80,6 +80,7 @@ EXPORTS = {
     "mantleCudaSampleRows": (C.c_int, [C.POINTER(SampleBatch), C.c_void_p, C.c_size_t, C.c_void_p]),
     "mantleCudaSamplerWorkspaceBytes": (C.c_int, [C.POINTER(SampleBatch), C.POINTER(C.c_size_t)]),
     "mantleCudaSamplerSplits": (C.c_int, [C.POINTER(SampleBatch), C.POINTER(C.c_int)]),
+    "mantleCudaSamplerKernelName": (C.c_char_p, [C.POINTER(SampleBatch)]),
     "mantleCudaRepeatPenaltyRowsF32": (C.c_int, [C.POINTER(SampleBatch), C.c_void_p]),
     "mantleCudaLogitPostprocessRowsF32": (
         C.c_int,

@@ -155,6 +155,7 @@ class BatchPlan:
         self.splits = s.value
         # kernels one launch() queues: the streaming kernel, plus the merge when a row is split
         self.kernels_per_launch = 1 if self.splits == 1 else 2
+        self.kernel_name = self.lib.mantleCudaSamplerKernelName(C.byref(b)).decode()
 
     def launch(self, stream=None):
         """Queues the batch on `stream` (default: torch's current stream).  Does not synchronise."""

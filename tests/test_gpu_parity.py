@@ -337,6 +337,57 @@ def test_top_k_beyond_bound_sets_status():
     assert g["next"][0] == -1 and 0 <= g["next"][1] < 1000
 
 
+def test_nan_logits_are_never_admitted_and_an_all_nan_row_is_flagged():
+    """NaN is outside the sampling contract (the reference's own answer depends on where in the row
+    the NaN sits, sampler.go:268-275).  What the library documents instead: a NaN never enters a
+    shortlist -- so a row with a few of them samples like the same row with those columns far below
+    everything else -- and a row holding nothing else returns token 0 with MANTLE_SAMPLE_STATUS_NAN."""
+    rng = np.random.default_rng(12)
+    rows, V = 6, 5000
+    lg = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    holes = rng.integers(0, V, size=(rows, 7))
+    with_nan, lowered = lg.copy(), lg.copy()
+    for r in range(rows):
+        with_nan[r, holes[r]] = np.nan
+        lowered[r, holes[r]] = -1e30
+    params = np.array([P(float(rng.random()), temperature=0.8, top_k=int(k), top_p=0.9, repeat_penalty=1.0)
+                       for k in (1, 5, 40, 40, 200, 1000)])
+    params[0]["greedy"] = 1
+    for max_k, splits in ((1000, 0), (1000, 3), (2000, 0)):  # streaming, split rows, long-shortlist kernel
+        g = run_gpu(torch.from_numpy(with_nan).to(DEV), params, max_k, splits=splits)
+        ref = O.sample_rows(lowered.copy(), params)
+        assert np.array_equal(g["next"], ref["next"]), (max_k, splits)
+        assert np.array_equal(g["cut"], ref["cut"]) and g["status"] == 0
+    allnan = np.full((2, 3000), np.nan, dtype=np.float32)
+    allnan[1] = lg[1, :3000]
+    for max_k in (40, 2000):
+        g = run_gpu(torch.from_numpy(allnan).to(DEV), params[2:4], max_k)
+        assert g["next"][0] == 0 and g["status"] == native.STATUS_NAN
+        assert g["next"][1] == O.sample_rows(allnan[1:2].copy(), params[3:4])["next"][0]
+
+
+def test_skipped_rows_are_not_sampled():
+    """`skip`: rows of a batched decode loop that have ended cost nothing and report token -1."""
+    rng = np.random.default_rng(13)
+    rows, V = 9, 40000
+    lg = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    params = np.array([P(float(rng.random()), temperature=0.8, top_k=30, top_p=0.9) for _ in range(rows)])
+    skip = (np.arange(rows) % 3 == 1).astype(np.int32)
+    ref = O.sample_rows(lg.copy(), params)
+    d = torch.from_numpy(lg).to(DEV)
+    p_dev = sampler.params_to_device(params, DEV)
+    skip_dev = torch.from_numpy(skip).to(DEV)
+    for max_k, splits in ((30, 1), (30, 0), (2000, 0)):
+        plan = sampler.BatchPlan(d, p_dev, max_k, splits=splits)
+        plan.batch.skip = skip_dev.data_ptr()
+        out = plan.launch()
+        torch.cuda.synchronize()
+        got = out.next.cpu().numpy()
+        assert np.array_equal(got[skip == 0], ref["next"][skip == 0]), (max_k, splits)
+        assert np.all(got[skip == 1] == -1) and np.all(out.n_kept.cpu().numpy()[skip == 1] == 0)
+        assert int(out.status.item()) == 0
+
+
 def test_outputs_do_not_overrun():
     rng = np.random.default_rng(8)
     rows, V = 5, 3000

@@ -136,6 +136,17 @@ def test_topk_order_and_ties():
     assert idx.tolist() == [2, 1, 0] and val.tolist() == [1.5, 1.0, 0.5]
 
 
+def test_nan_is_admitted_while_the_shortlist_has_room():
+    """The reference's topK on NaN (sampler.go:268-275): `topVal[pos-1] < v` is false on either
+    side of a NaN, so a NaN is appended while the list has room and then shields everything
+    before it from later, larger values.  The answer depends on where the NaN sits, which is why
+    NaN logits are outside the sampling contract; the oracle restates the behaviour as it is."""
+    idx, val = O.topk([np.nan, 1.0, 2.0], 2, 1.0)
+    assert idx.tolist() == [0, 2] and np.isnan(val[0]) and val[1] == 2.0
+    idx, val = O.topk([1.0, 2.0, np.nan], 2, 1.0)  # the list is full when the NaN arrives: dropped
+    assert idx.tolist() == [1, 0]
+
+
 def test_topk1_with_temperature_takes_full_path():
     out, _ = run1([1.0, 2.0, 0.5], uniform=0.99, temperature=0.5, top_k=1, top_p=1.0)
     assert out["next"][0] == 1 and out["n_kept"][0] == 1 and out["cut"][0] == 1
