@@ -51,6 +51,7 @@
 #include "sampler_rows.cuh"
 #include "scan_rows_ldg.cuh"
 #include "wide_rows.cuh"
+#include "wide_rows_fast.cuh"
 #include "merge_parts.cuh"
 
 namespace {
@@ -253,19 +254,27 @@ int launch_merge(KArgs& a, cudaStream_t stream) {
     return (int)cudaGetLastError();
 }
 
-int launch_wide(const KArgs& a, int dtype, cudaStream_t stream) {
+// Long shortlists: wide_hist_kernel settles the rows, wide_rows_kernel behind it takes the few it
+// marks as unsettled (and returns at once for all others).
+template <typename T>
+int launch_wide_as(const KArgs& a, cudaStream_t stream) {
     static std::atomic<int> granted[2][kMaxDevices];
-    const size_t smem = ((sizeof(WideCtl) + 127) / 128) * 128 + bitmap_words(a.vocab) * sizeof(uint32_t);
-    if (dtype == MANTLE_DTYPE_F32) {
-        const int rc = ensure_smem(wide_rows_kernel<float>, smem, granted[0]);
-        if (rc) return rc;
-        wide_rows_kernel<float><<<a.rows, WIDE_NT, smem, stream>>>(a);
-    } else {
-        const int rc = ensure_smem(wide_rows_kernel<bf16_t>, smem, granted[1]);
-        if (rc) return rc;
-        wide_rows_kernel<bf16_t><<<a.rows, WIDE_NT, smem, stream>>>(a);
-    }
+    const size_t bitmap = bitmap_words(a.vocab) * sizeof(uint32_t);
+    const size_t smem_hist = WF_CTL_BYTES + 2 * (size_t)WF_BINS * 4 + (size_t)WF_CAND * 8 + bitmap;
+    const size_t smem_rows = ((sizeof(WideCtl) + 127) / 128) * 128 + bitmap;
+    int rc = ensure_smem(wide_hist_kernel<T>, smem_hist, granted[0]);
+    if (rc) return rc;
+    rc = ensure_smem(wide_rows_kernel<T>, smem_rows, granted[1]);
+    if (rc) return rc;
+    wide_hist_kernel<T><<<a.rows, WF_NT, smem_hist, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    wide_rows_kernel<T><<<a.rows, WIDE_NT, smem_rows, stream>>>(a);
     return (int)cudaGetLastError();
+}
+
+int launch_wide(const KArgs& a, int dtype, cudaStream_t stream) {
+    return dtype == MANTLE_DTYPE_F32 ? launch_wide_as<float>(a, stream) : launch_wide_as<bf16_t>(a, stream);
 }
 
 int launch_penalty(const KArgs& a, cudaStream_t stream) {
@@ -304,7 +313,7 @@ extern "C" int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* spli
 
 extern "C" const char* mantleCudaSamplerKernelName(const MantleSampleBatch* batch) {
     if (!batch_ok(batch, true)) return "";
-    return batch->max_top_k > KMAX ? "wide_rows_kernel" : "scan_rows_ldg_kernel";
+    return batch->max_top_k > KMAX ? "wide_hist_kernel" : "scan_rows_ldg_kernel";
 }
 
 extern "C" int mantleCudaSamplerWorkspaceBytes(const MantleSampleBatch* batch, size_t* bytes) {

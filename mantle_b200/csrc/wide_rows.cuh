@@ -1,4 +1,5 @@
-// wide_rows_kernel: shortlists longer than 1024 entries, up to the whole vocabulary.
+// wide_rows_kernel: shortlists longer than 1024 entries, up to the whole vocabulary -- the
+// thorough kernel behind wide_hist_kernel, for the rows that one leaves unsettled.
 // Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
 // translation unit.
 #pragma once
@@ -24,12 +25,13 @@ namespace {
 // prefix can differ from the reference's in the last bits (about 1e-16 relative), which moves a
 // token only when r lies that close to a boundary -- far inside the contract's 1e-6.
 // The row is read once per pass (11 to 30 passes; it stays in L2 after the first), so this
-// path is compute-bound by design and meant for the rare request, not for throughput.
+// kernel is compute-bound by design.  It is launched behind wide_hist_kernel (three to five
+// passes) and takes only the rows that kernel marked as unsettled: ties by the thousand around
+// the place where the walk stops, rows with an infinite maximum, rows of nothing but NaN.
 
 constexpr int WIDE_NT = 512;
-#ifndef WIDE_MINB
-#define WIDE_MINB 2  // two CTAs per SM at 64 registers: 3 to 15 % faster than one at 128, spills included
-#endif
+constexpr int WIDE_UNRESOLVED = (int)0x80000000;  // next[row] of a row wide_hist_kernel left to this kernel
+constexpr int WIDE_MINB = 2;  // two CTAs per SM at 64 registers: 3 to 15 % faster than one at 128, spills included
 constexpr int WIDE_FAN = 16;  // sub-ranges per pass (4 key bits)
 
 struct WideCtl {
@@ -73,10 +75,7 @@ __global__ void __launch_bounds__(WIDE_NT, WIDE_MINB) wide_rows_kernel(const KAr
     const int row = blockIdx.x;
     const int V = a.vocab;
 
-    if (a.skip && a.skip[row] != 0) {
-        if (tid == 0) publish_row(a, row, -1);
-        return;
-    }
+    if (a.next[row] != WIDE_UNRESOLVED) return;  // settled by wide_hist_kernel (skipped rows included)
     const MantleSampleParams P = row_params(a, row);
     bool greedy, bad_k;
     const int k = row_k(a, P, 0x7fffffff, &greedy, &bad_k);  // no cap on this path

@@ -154,7 +154,7 @@ class BatchPlan:
         native.check(self.lib.mantleCudaSamplerSplits(C.byref(b), C.byref(s)), "Splits")
         self.splits = s.value
         # kernels one launch() queues: the streaming kernel, plus the merge when a row is split
-        self.kernels_per_launch = 1 if self.splits == 1 else 2
+        self.kernels_per_launch = 2 if (self.splits > 1 or max_top_k > native.MAX_TOP_K) else 1
         self.kernel_name = self.lib.mantleCudaSamplerKernelName(C.byref(b)).decode()
 
     def launch(self, stream=None):
