@@ -6,9 +6,14 @@
 namespace {
 
 // Merge of `parts` local shortlists per row (several CTAs of one GPU, or one per
-// vocabulary shard after an all-gather), then the tail.
-__global__ void __launch_bounds__(ShapeK1024::NT, ShapeK1024::MINB) merge_parts_kernel(const KArgs a) {
-    using S = ShapeK1024;
+// vocabulary shard after an all-gather), then the tail.  In the small shape (256 threads, four
+// CTAs per SM) when parts * top_k fits its buffer, else in the large one.
+// Launched behind the kernel that writes the parts, where possible as a programmatic dependent
+// launch: everything above griddepcontrol.wait (parameters, the control block) runs while that
+// kernel drains, and the wait returns once its writes are visible.  Without the launch attribute
+// the wait is a no-op.
+template <class S>
+__global__ void __launch_bounds__(S::NT, S::MINB) merge_parts_kernel(const KArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Cand* buf = reinterpret_cast<Cand*>(smem_raw);
     uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
@@ -26,6 +31,7 @@ __global__ void __launch_bounds__(ShapeK1024::NT, ShapeK1024::MINB) merge_parts_
     const bool bad_k = !greedy && (k > a.max_top_k || k > KMAX || k < 1);
 
     if (tid == 0) ctl->cnt = 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // Every part is in order, so its j-th value is reached by j of its entries: with
     // j = ceil(k / parts) the smallest of the parts' j-th values is reached by at least k entries
     // overall and bounds the k-th largest from below.  Only entries that reach it are gathered --
@@ -71,10 +77,9 @@ __global__ void __launch_bounds__(ShapeK1024::NT, ShapeK1024::MINB) merge_parts_
         }
         return;
     }
-    bool have, ordered;
-    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
+    final_topk<S>(buf, ctl, hist, k, tid);
     __syncthreads();
-    finish_row<S, MODE_FUSED>(a, row, 0, P, greedy, ordered, buf, ctl, tid);
+    finish_row<S, MODE_FUSED>(a, row, 0, P, greedy, buf, ctl, tid);
 }
 
 }  // namespace

@@ -243,15 +243,35 @@ int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
     return launch_scan_shape<ShapeK1024, MODE>(a, dtype, stream);
 }
 
-int launch_merge(KArgs& a, cudaStream_t stream) {
+// `dependent`: the merge directly follows, on the same stream, the kernel that writes its parts;
+// it is then launched programmatically dependent on that kernel, so that its start-up overlaps
+// the other's end (the merge waits with griddepcontrol.wait before it reads a part).
+template <class S>
+int launch_merge_as(const KArgs& a, cudaStream_t stream, bool dependent) {
     static std::atomic<int> granted[kMaxDevices];
+    const size_t smem = S::SMEM_FIXED;
+    const int rc = ensure_smem(merge_parts_kernel<S>, smem, granted);
+    if (rc) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)a.rows);
+    cfg.blockDim = dim3((unsigned)S::NT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, merge_parts_kernel<S>, a);
+}
+
+int launch_merge(KArgs& a, cudaStream_t stream, bool dependent = false) {
     if (a.part_stride == 0) a.part_stride = (long long)a.rows * a.part_cap;
     if (a.cnt_stride == 0) a.cnt_stride = a.rows;
-    const size_t smem = ShapeK1024::SMEM_FIXED;
-    const int rc = ensure_smem(merge_parts_kernel, smem, granted);
-    if (rc) return rc;
-    merge_parts_kernel<<<a.rows, ShapeK1024::NT, smem, stream>>>(a);
-    return (int)cudaGetLastError();
+    const long long held = (long long)a.parts * std::min(a.part_cap, a.max_top_k);
+    if (a.max_top_k <= ShapeK256::KCAP && held <= ShapeK256::CAP / 2)
+        return launch_merge_as<ShapeK256>(a, stream, dependent);
+    return launch_merge_as<ShapeK1024>(a, stream, dependent);
 }
 
 // Long shortlists: wide_hist_kernel settles the rows, wide_rows_kernel behind it takes the few it
@@ -347,7 +367,7 @@ extern "C" int mantleCudaSampleRows(const MantleSampleBatch* batch, void* worksp
     a.part_cnt = a.part_idx + n * a.part_cap;
     rc = launch_scan<MODE_PARTS>(a, batch->dtype, stream);
     if (rc) return rc;
-    return launch_merge(a, stream);
+    return launch_merge(a, stream, true);
 }
 
 extern "C" int mantleCudaRepeatPenaltyRowsF32(const MantleSampleBatch* batch, mantleCudaStream_t stream_) {

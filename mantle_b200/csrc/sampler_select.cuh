@@ -218,21 +218,55 @@ __device__ __forceinline__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* 
     return select_topk<S>(buf, ctl, hist, k, tid, have_kth);
 }
 
-// Orders the n <= KCAP entries of the buffer (key descending, index ascending) by
-// counting, into sval/sidx.  Entries are distinct under that order, so ranks are a
-// permutation.
+// a precedes b in the shortlist order (key descending, index ascending)
+__device__ __forceinline__ bool cand_before(const Cand& a, const Cand& b) {
+    return a.key > b.key || (a.key == b.key && a.idx < b.idx);
+}
+
+// Bitonic sort of the first n entries of the buffer into the shortlist order, in place; the
+// buffer has room for the next power of two (n <= CAP / 2).
 template <class S>
-__device__ void rank_sort(const Cand* buf, int n, float* sval, int32_t* sidx, int tid) {
-    for (int i = tid; i < n; i += S::NT) {
-        Cand me = buf[i];
-        int rank = 0;
-        for (int j = 0; j < n; j++) {
-            Cand o = buf[j];
-            rank += (o.key > me.key || (o.key == me.key && o.idx < me.idx)) ? 1 : 0;
+__device__ void sort_buf(Cand* buf, int n, int tid) {
+    int n2 = 32;
+    while (n2 < n) n2 <<= 1;
+    Cand last;  // behind every real entry
+    last.key = 0u;
+    last.idx = 0xffffffffu;
+    for (int i = n + tid; i < n2; i += S::NT) buf[i] = last;
+    __syncthreads();
+    for (int kk = 2; kk <= n2; kk <<= 1) {
+        for (int jj = kk >> 1; jj > 0; jj >>= 1) {
+            for (int i = tid; i < n2; i += S::NT) {
+                const int ixj = i ^ jj;
+                if (ixj > i) {
+                    const Cand x0 = buf[i], x1 = buf[ixj];
+                    const bool up = (i & kk) == 0;  // this pair is put into shortlist order
+                    if (up ? cand_before(x1, x0) : cand_before(x0, x1)) {
+                        buf[i] = x1;
+                        buf[ixj] = x0;
+                    }
+                }
+            }
+            __syncthreads();
         }
-        sval[rank] = key2f(me.key);
-        sidx[rank] = (int32_t)me.idx;
     }
+}
+
+// The final cut of a row (or of a merge): the k best entries, in order.  Small buffers come out of
+// the counting select in order; larger ones are cut by the radix select and then sorted.  Called by
+// every thread with the buffer quiescent.
+//
+// (Measured and not kept: ranking only the newcomers of a cut against the ordered prefix the
+// previous cut left -- by binary search, or with a histogram of their positions -- takes a third
+// of the counting select's instructions and was 10 to 25 % slower at every shortlist length: a
+// CTA streams nothing while it cuts, so what counts is the cut's longest dependent chain, and the
+// counting select's is one independent read per entry.)
+template <class S>
+__device__ __forceinline__ void final_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid) {
+    bool have, ordered;
+    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
+    __syncthreads();
+    if (!ordered) sort_buf<S>(buf, min(ctl->cnt, S::KCAP), tid);
 }
 
 }  // namespace
