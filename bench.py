@@ -439,6 +439,10 @@ def run_ours(args):
     if args.workload == "vocab_sharded":
         return run_vocab_sharded(args, world, rank, device)
     w = workloads.make(args.workload, rows=args.rows, device=device, seed=workloads.BASE_SEED + 3000 + rank)
+    if args.top_k > 0:  # a side measurement of another shortlist length: the device arm only
+        w.params["top_k"] = args.top_k
+        w.max_top_k = min(args.top_k, w.vocab)
+        args.no_e2e = args.no_cpu = True
     p_dev = sampler.params_to_device(w.params, device)
     post = bool(args.logit_scale or args.logit_softcap)
     if post:  # a side measurement of the fused head post-processing: the device arm only
@@ -521,7 +525,7 @@ def run_ours(args):
         kernel_bytes = w.rows * w.bytes_per_row  # one launch, one GPU
         achieved = kernel_bytes / (ms / 1e3) / 1e9
         kernel = plan.kernel_name
-        ratio = dram_traffic_ratio(kernel) if args.workload == "throughput" and not post else None
+        ratio = dram_traffic_ratio(kernel) if args.workload == "throughput" and not post and not args.top_k else None
         line = {
             "metric": METRIC, "value": rows_total / (ms / 1e3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
@@ -534,6 +538,7 @@ def run_ours(args):
                       ("inputs (%.1f MB) fit the 126 MB L2 and are not flushed: an L2-resident timing" % (kernel_bytes / 1e6)),
                 "ctas_per_row": plan.splits,
                 **({"logit_scale": args.logit_scale, "logit_softcap": args.logit_softcap} if post else {}),
+                **({"top_k_override": args.top_k} if args.top_k > 0 else {}),
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -605,6 +610,7 @@ def main():
     ap.add_argument("--splits", type=int, default=0, help="CTAs per row (0: library's choice)")
     ap.add_argument("--logit-scale", type=float, default=0.0, help="fuse the model head's multiplier (side measurement)")
     ap.add_argument("--logit-softcap", type=float, default=0.0, help="fuse the model head's soft cap (side measurement)")
+    ap.add_argument("--top-k", type=int, default=0, help="override every row's top_k (side measurement)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -13,21 +13,24 @@ package inference
 //
 //	ds, canDeviceSample := g.Model.(deviceSampler)
 //
-// and in the loop, before the host path (engine.go:291-300):
+// and in the loop, between the device-greedy branch (engine.go:284-289) and the host path
+// (engine.go:291-300):
 //
 //	} else if canDeviceSample {
-//		next, err = safeForwardTokenSample(ds, next, g.Sampler.NextDeviceParams(), toks, g.StopTokens)
+//		next, err = g.stepDeviceSample(ds, next, toks)
 //
-// The model's ForwardTokenSample runs the layers as ForwardTokenGreedy does
-// (simd/runtime_greedy.go:13-44), leaves the LM-head output on the device
-// (Ops.DeviceMatVecNoCopy, cuda/ops.go:1289-1330) and calls Ops.DeviceSampleLastResult, which
-// hands greedyResultDev to native.SampleRowsF32 the way DeviceArgMaxLastResult hands it to
-// native.ArgMaxF32 (cuda/ops.go:1332-1346).  Errors are parked with recordFastPathErrorLocked
-// like every other fast path.
+// The model's ForwardTokenSample (cuda.go -> simd/runtime_sample.go) runs the layers as
+// ForwardTokenGreedy does, leaves the LM-head output on the device (Ops.DeviceMatVecNoCopy,
+// cuda/ops.go:1289-1330) and calls Ops.DeviceSampleLastResult, which hands greedyResultDev to
+// native.SampleRows the way DeviceArgMaxLastResult hands it to native.ArgMaxF32
+// (cuda/ops.go:1332-1346).  Errors are parked with recordFastPathErrorLocked like every other
+// fast path.
 
 import (
+	"errors"
 	"fmt"
 
+	"github.com/samcharles93/mantle/internal/backend/simd"
 	"github.com/samcharles93/mantle/internal/logits"
 )
 
@@ -42,4 +45,30 @@ func safeForwardTokenSample(m deviceSampler, id int, p logits.DeviceParams, rece
 		}
 	}()
 	return m.ForwardTokenSample(id, p, recent, exclude)
+}
+
+// stepDeviceSample is one iteration of the loop with the sample taken on the device: the
+// sampler's generator is advanced once (NextDeviceParams), and when the device path is not
+// available for this step the host path runs with that same draw.
+func (g *Generator) stepDeviceSample(ds deviceSampler, tok int, toks []int) (int, error) {
+	p := g.Sampler.NextDeviceParams()
+	next, err := safeForwardTokenSample(ds, tok, p, toks, g.StopTokens)
+	if err == nil || !errors.Is(err, simd.ErrNoDeviceSampler) {
+		return next, err
+	}
+	logitsVec, err := g.Model.ForwardToken(tok) // the reference's own step (engine.go:291-295)
+	if err != nil {
+		return 0, err
+	}
+	return safeSampleWith(g.Sampler, logitsVec, toks, g.StopTokens, p)
+}
+
+// safeSampleWith is safeSample (engine.go:339-346) around SampleWithParams.
+func safeSampleWith(s *logits.Sampler, logitsVec []float32, recent, exclude []int, p logits.DeviceParams) (next int, err error) {
+	defer func() {
+		if rec := recover(); rec != nil {
+			err = fmt.Errorf("panic in Sample: %v", rec)
+		}
+	}()
+	return s.SampleWithParams(logitsVec, recent, exclude, p), nil
 }

@@ -3,7 +3,11 @@
 package logits
 
 // Additive to sampler.go: what the inference loop needs to run Sample on the device.
-// Not compiled here (no Go toolchain); see INTEGRATION.md.
+// Not compiled here (no Go toolchain).
+//
+// One change to sampler.go itself goes with it: the field `rng *rand.Rand` (sampler.go:47) becomes
+// `rng interface{ Float64() float64 }`, which *rand.Rand satisfies, so that SampleWithParams below
+// can replay a draw that NextDeviceParams already took.
 
 // DeviceParams are the values NewSampler left in the Sampler, for one step.
 type DeviceParams struct {
@@ -30,4 +34,20 @@ func (s *Sampler) NextDeviceParams() DeviceParams {
 		p.Uniform = s.rng.Float64()
 	}
 	return p
+}
+
+// constDraw replays one uniform.
+type constDraw float64
+
+func (c constDraw) Float64() float64 { return float64(c) }
+
+// SampleWithParams is Sample for a step whose parameters were already taken with NextDeviceParams
+// but whose device path turned out to be unavailable: the same computation as Sample on the host
+// logits, with the uniform p carries instead of a fresh draw, so that the generator advances
+// exactly once per step either way.
+func (s *Sampler) SampleWithParams(logits []float32, recent []int, excludePenalty []int, p DeviceParams) int {
+	saved := s.rng
+	s.rng = constDraw(p.Uniform)
+	defer func() { s.rng = saved }()
+	return s.Sample(logits, recent, excludePenalty)
 }

@@ -77,9 +77,10 @@ __global__ void __launch_bounds__(S::NT, S::MINB) merge_parts_kernel(const KArgs
         }
         return;
     }
-    final_topk<S>(buf, ctl, hist, k, tid);
+    bool have, ordered;
+    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
     __syncthreads();
-    finish_row<S, MODE_FUSED>(a, row, 0, P, greedy, buf, ctl, tid);
+    finish_row<S, MODE_FUSED>(a, row, 0, P, greedy, ordered, buf, ctl, tid);
 }
 
 }  // namespace

@@ -218,9 +218,11 @@ __device__ __forceinline__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* 
     return select_topk<S>(buf, ctl, hist, k, tid, have_kth);
 }
 
-// a precedes b in the shortlist order (key descending, index ascending)
-__device__ __forceinline__ bool cand_before(const Cand& a, const Cand& b) {
-    return a.key > b.key || (a.key == b.key && a.idx < b.idx);
+// a precedes b in the shortlist order (key descending, index ascending).  By value and without
+// short-circuits: an entry read through a reference to shared memory became two dependent loads
+// and a branch per compare, which cost the split-row batches a seventh of their time.
+__device__ __forceinline__ bool cand_before(const Cand a, const Cand b) {
+    return (a.key > b.key) | ((a.key == b.key) & (a.idx < b.idx));
 }
 
 // Bitonic sort of the first n entries of the buffer into the shortlist order, in place; the
@@ -252,21 +254,27 @@ __device__ void sort_buf(Cand* buf, int n, int tid) {
     }
 }
 
-// The final cut of a row (or of a merge): the k best entries, in order.  Small buffers come out of
-// the counting select in order; larger ones are cut by the radix select and then sorted.  Called by
-// every thread with the buffer quiescent.
-//
-// (Measured and not kept: ranking only the newcomers of a cut against the ordered prefix the
-// previous cut left -- by binary search, or with a histogram of their positions -- takes a third
-// of the counting select's instructions and was 10 to 25 % slower at every shortlist length: a
-// CTA streams nothing while it cuts, so what counts is the cut's longest dependent chain, and the
-// counting select's is one independent read per entry.)
+// Orders the n entries of the buffer (key descending, index ascending) by counting, into
+// sval/sidx.  Entries are distinct under that order, so ranks are a permutation.  One independent
+// read per entry and thread: n * n / NT steps, the shorter chain up to a few hundred entries.
 template <class S>
-__device__ __forceinline__ void final_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid) {
-    bool have, ordered;
-    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
-    __syncthreads();
-    if (!ordered) sort_buf<S>(buf, min(ctl->cnt, S::KCAP), tid);
+__device__ void rank_sort(const Cand* buf, int n, float* sval, int32_t* sidx, int tid) {
+    for (int i = tid; i < n; i += S::NT) {
+        Cand me = buf[i];
+        int rank = 0;
+        for (int j = 0; j < n; j++) {
+            const Cand o = buf[j];
+            rank += cand_before(o, me) ? 1 : 0;
+        }
+        sval[rank] = key2f(me.key);
+        sidx[rank] = (int32_t)me.idx;
+    }
 }
+
+// (Measured and not kept for the cuts of the streaming loop: ranking only the newcomers of a cut
+// against the ordered prefix the previous cut left -- by binary search, or with a histogram of
+// their positions -- takes a third of the counting select's instructions and was 10 to 25 %
+// slower at every shortlist length: a CTA streams nothing while it cuts, so what counts is the
+// cut's longest dependent chain, and the counting select's is one independent read per entry.)
 
 }  // namespace

@@ -227,24 +227,32 @@ __device__ void sample_tail_warp(const KArgs& a, int row, const MantleSamplePara
     if (lane == 0) publish_row(a, row, token, n_kept, cut, tprob, sum_out);
 }
 
-// After the final cut left the shortlist in order: finish the row or publish the local
-// shortlist.  The value / id / probability arrays live in the part of the candidate buffer the
-// shortlist (at most KCAP entries) does not occupy.
+// After the final cut: order the survivors where the cut did not (`ordered`: it did) and either
+// finish the row or publish the local shortlist.  The value / id / probability arrays live in the
+// part of the candidate buffer the shortlist (at most KCAP entries) does not occupy.
 template <class S, int MODE>
 __device__ void finish_row(const KArgs& a, int row, int split, const MantleSampleParams& P, bool greedy,
-                           Cand* buf, Ctl* ctl, int tid) {
+                           bool ordered, Cand* buf, Ctl* ctl, int tid) {
     constexpr int KC = S::KCAP;
     const int n = min(ctl->cnt, KC);
     float* sval = reinterpret_cast<float*>(buf + KC);
     int32_t* sidx = reinterpret_cast<int32_t*>(sval + KC);
     double* sprob = reinterpret_cast<double*>(sidx + KC);
-    if (MODE == MODE_FUSED && n <= 64) {
+    if (MODE == MODE_FUSED && ordered && n <= 64) {
         if (tid < 32) sample_tail_warp(a, row, P, greedy, n, buf, sidx, sprob, tid);
         return;
     }
-    for (int i = tid; i < n; i += S::NT) {
-        sval[i] = key2f(buf[i].key);
-        sidx[i] = (int32_t)buf[i].idx;
+    if (!ordered && n > 512) {  // counting would take n * n / NT steps: sort in place instead
+        sort_buf<S>(buf, n, tid);
+        ordered = true;
+    }
+    if (ordered) {
+        for (int i = tid; i < n; i += S::NT) {
+            sval[i] = key2f(buf[i].key);
+            sidx[i] = (int32_t)buf[i].idx;
+        }
+    } else {
+        rank_sort<S>(buf, n, sval, sidx, tid);
     }
     __syncthreads();
     if (MODE == MODE_FUSED) {

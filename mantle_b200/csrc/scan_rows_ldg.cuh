@@ -96,14 +96,9 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     __syncthreads();
 
     // ---- stream the item ------------------------------------------------------------------
-#ifdef MANTLE_DEBUG_SWITCHES
-    const int tmode = (a.debug >> 4) & 0xf;
-    const int tadd = tmode == 1 ? max(k >> 2, 16) : tmode == 2 ? max(k, 16) : tmode == 3 ? 16 : tmode == 4 ? 32
-                   : tmode == 5 ? max(k >> 1, 32) : tmode == 6 ? max(k >> 2, 8) : max(k >> 1, 16);
-    const int trig = min(k + tadd, CAP / 2);
-#else
-    const int trig = min(k + max(k >> 1, 16), CAP / 2);  // cut the buffer at this many entries
-#endif
+    // cut the buffer at this many entries (measured: k + k/4, k + k, k + 16 and k + 32 are all within
+    // 2 % of this up to top_k 100 and worse beyond; votes every third region gain 2 % from top_k 64 on)
+    const int trig = min(k + max(k >> 1, 16), CAP / 2);
     float thr = __uint_as_float(0xff800000u);            // -inf
     float rthr = thr;  // POST: the raw logit every column that can reach thr has at least
     const Post& POSTP = a.post;
@@ -203,55 +198,28 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         region_end(k + 1);
 
         // -- regions 1.. : two register sets, each refilled while the other is filtered --
-        // Between the first region and the end of the item the warps meet only when the buffer wants
-        // a cut: a warp that finds the buffer at `trig` entries at the end of a region goes to the
-        // barrier, the others find the same at the end of theirs and follow (the count only falls
-        // in a cut), and warps that have finished their regions wait there already.  Every meeting
-        // is one event for the whole CTA, so all threads agree on what it decides.  A warp decides
-        // as one (a vote over its lanes, which also brings them back together after the survivors'
-        // divergent paths): lanes of one warp must never reach a barrier apart.
-#ifdef MANTLE_DEBUG_SWITCHES
-        int dbg_cuts = 0, dbg_cut_n = 0;
-#endif
-        auto wants_cut = [&]() { return __any_sync(0xffffffffu, live_count(ctl) >= trig) != 0; };
-        auto meet = [&](bool finished) -> bool {
-            const int nfin = __syncthreads_count(finished ? 1 : 0);
-            const int n = live_count(ctl);  // nobody appends between these two barriers
-            __syncthreads();
-            if (n > CAP) {
-                careful = true;  // entries were dropped: redo the item on the careful path
-            } else if (n >= trig && nfin < NT) {
-#ifdef MANTLE_DEBUG_SWITCHES
-                dbg_cuts++; dbg_cut_n += n;
-#endif
-                bool have;
-                uint32_t kth = refresh_topk<S>(buf, ctl, hist, k, tid, &have);
-                if (have) {
-                    thr = key2f(kth);
-                    if (POST) rthr = post_raw_bound(thr, c.inv_temp, POSTP);
-                }
-            }
-            return nfin == NT;
-        };
+        // The barrier carries only the vote (the register sets are private), so it need not follow
+        // every region: the threshold is refreshed at most every VOTE_EVERY regions, at the price of
+        // a few more survivors under a threshold that is that much staler.
+        // (Measured and not kept: no periodic barrier at all -- a warp that finds the buffer at `trig`
+        // entries goes to the barrier and the others follow when they find the same, warps of one CTA
+        // drifting apart in between.  2 to 5 % faster at top_k 40 to 64, 1 to 2.5 % slower at 20 and
+        // 100, slower on the split-row batches.  Such a scheme must take the decision with a warp-wide
+        // vote: lanes of one warp that read the count at different moments reached different barrier
+        // instructions, which hung the kernel until the process was killed.)
         int r = 1;
         while (r < nreg && !careful) {
             if (r + 1 < nreg) load(ra, r + 1);
             ahead(r + 3);
             later(rb, r);
-            if (wants_cut()) meet(false);
+            if (r % VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
             if (++r >= nreg || careful) break;
             if (r + 1 < nreg) load(rb, r + 1);
             ahead(r + 3);
             later(ra, r);
-            if (wants_cut()) meet(false);
+            if (r % VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
             ++r;
         }
-        while (!careful && !meet(true)) {
-        }
-#ifdef MANTLE_DEBUG_SWITCHES
-        if ((a.debug & 0x100) && tid == 0 && blockIdx.x < 4)
-            printf("row %d k %d trig %d: cuts %d, entries cut %d, left %d\n", row, k, trig, dbg_cuts, dbg_cut_n, live_count(ctl));
-#endif
     }
 
     if (!careful) {
@@ -310,7 +278,8 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         __syncthreads();
     }
 
-    final_topk<S>(buf, ctl, hist, k, tid);  // the shortlist, in order
+    bool have, ordered;
+    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
     __syncthreads();
     if (bad_k) {
         if (tid == 0) {
@@ -323,7 +292,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         }
         return;
     }
-    finish_row<S, MODE>(a, row, split, P, greedy, buf, ctl, tid);
+    finish_row<S, MODE>(a, row, split, P, greedy, ordered, buf, ctl, tid);
 }
 
 }  // namespace
