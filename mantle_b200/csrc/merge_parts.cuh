@@ -17,7 +17,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) merge_parts_kernel(const KArgs
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Cand* buf = reinterpret_cast<Cand*>(smem_raw);
     uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
-    Ctl* ctl = reinterpret_cast<Ctl*>(hist + 256);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + S::CTL_OFF);
     const int tid = threadIdx.x;
     const int row = blockIdx.x;
 

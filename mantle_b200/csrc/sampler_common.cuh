@@ -8,6 +8,7 @@ namespace {
 
 constexpr int KMAX = MANTLE_SAMPLE_MAX_TOP_K;
 constexpr int RANK_MAX = 256;  // largest buffer the counting select takes
+constexpr int HBINS = 256;     // bins of the running histogram of the candidate buffer
 
 // Launch shape of one kernel instantiation.
 //   NT    threads per CTA            U     16-byte vectors per thread per region
@@ -24,18 +25,25 @@ struct Shape {
     static_assert(KCAP + NT * SLOW_EPT <= CAP, "careful path needs room for one full step");
     static_assert(KCAP * 24 <= CAP * 8, "ordered shortlist must fit behind the survivors");
     static_assert(RANK_MAX <= NT, "counting select: one entry per thread");
-    // shared memory: [Cand buf[CAP]] [hist[256]] [Ctl] [bitmap]
-    static constexpr size_t SMEM_FIXED = 8 * (size_t)CAP + 4 * 256 + 512;
+    // shared memory: [Cand buf[CAP]] [hist[HBINS]] [Ctl] [staged survivors[NWARP][STG]] [their counts[NWARP]] [bitmap]
+    static constexpr int STG = 32;  // raw survivors a warp sets aside before it works them off together
+    static constexpr size_t CTL_OFF = 8 * (size_t)CAP + 4 * (size_t)HBINS;
+    static constexpr size_t STG_OFF = CTL_OFF + 512;
+    static constexpr size_t WCNT_OFF = STG_OFF + 8 * (size_t)(NWARP * STG);
+    static constexpr size_t SMEM_FIXED = WCNT_OFF + ((4 * (size_t)NWARP + 15) & ~(size_t)15);
+    // the streaming loop compacts the buffer at its next meeting once it holds this many entries
+    static constexpr int FORCE = CAP / 2;
 };
 // Four small CTAs per SM overlap the serial phases of a row (bitmap, cuts, tail) with the
 // streaming of three other rows; measured against three CTAs fed by a ring of bulk copies
 // (0.541 against 0.403 ms for 4096 rows of 151 936 float32 columns at top_k 20) and against
 // larger CTAs at every shortlist length.
 using ShapeK256 = Shape<256, 4, 2048, 256, 4>;    // top_k <= 256: 16 KB candidate buffer, four CTAs per SM
-using ShapeK1024 = Shape<512, 4, 4096, KMAX, 1>;  // top_k <= 1024: 32 KB candidate buffer; also the merge kernel
+using ShapeK1024 = Shape<256, 4, 4096, KMAX, 4>;  // top_k <= 1024: 32 KB candidate buffer
+using ShapeMerge = Shape<512, 4, 4096, KMAX, 1>;  // the merge kernel where the parts hold more than ShapeK256 takes
 constexpr int VOTE_EVERY = 2;  // regions between two "does the buffer need a cut" votes
 constexpr int MAX_NWARP = 32;
-constexpr int MERGE_CAP = ShapeK1024::CAP;
+constexpr int MERGE_CAP = ShapeMerge::CAP;
 
 constexpr int POST_SCALE = 1, POST_CAP = 2, POST_TANHF = 4;
 
@@ -57,6 +65,20 @@ struct Ctl {
     int n_after;        // shortlist length after min-p
     int cut;
     int pos;
+    int k;              // shortlist length wanted (for the warp that refreshes the threshold)
+    // running histogram of the buffer's values: bin = (v - hbase) * hscale, clamped to [0, HBINS)
+    uint32_t thr_key;   // key of the admission threshold: at least k buffered entries reach it
+    float thr;          // the same as a value, for the streaming loop (any value once valid stays valid)
+    float hbase, hscale;  // read as one float2
+    float htop;
+    float hwidth;       // 1 / hscale
+    int walked;         // entries in the buffer when the histogram was last walked
+    // what the out-of-line survivor code needs to know about the row
+    int pen_on;         // the penalty is applied from the bitmap
+    float inv_temp, pen;
+    int voff;           // global id of column 0
+    int post_mode;
+    float post_scale, post_cap;
     int pad;
     double sum;
     double new_sum;
@@ -289,109 +311,200 @@ __device__ __forceinline__ void append(Cand* buf, Ctl* ctl, float v, int gidx) {
     }
 }
 
-// One column whose scaled RAW value reached the filter.  The penalty only ever lowers a
-// logit (l/p < l for l > 0, l*p < l for l < 0, p > 1), so filtering raw values first is
-// conservative: only here, on the rare survivor, is the bitmap consulted, the penalty
-// applied and the filter repeated on the true value.
-// A survivor that carries a penalty is rarer still (a column of the history window among the few
-// that pass the filter); its divide lives out of line, once per kernel, so that the streaming
-// loop stays small.  The candidate buffer and the control block sit at fixed offsets.
+// ---------------------------------------------------------------------------------------
+// The running histogram.  While a row streams, every entry that enters the candidate buffer is
+// also counted in one of HBINS bins of its value.  The bin is a non-decreasing map of the value, so
+// walking the counts from the top bin down to the bin b where they reach k gives a threshold --
+// the lower edge of bin b -- that at least k buffered entries reach, without a barrier and without
+// touching the buffer: one warp does it after every region while the others stream on.  A column
+// below such a threshold is below k buffered entries and can be in no shortlist; a column AT it
+// may be (the entries that reach the threshold can have higher indices), so admission is `>=`.
+__device__ __forceinline__ int hist_bin(float v, float base, float scale) {
+    const float d = __fmul_rn(__fsub_rn(v, base), scale);
+    return d > 0.0f ? (d < (float)(HBINS - 1) ? (int)d : HBINS - 1) : 0;  // NaN (inf - inf, inf * 0): bin 0
+}
+
+// The buffer entry and its count.  A count seen by the warp that walks the histogram stands for
+// an entry that is in the buffer by the next barrier, which is before anything reads the buffer.
 template <class S>
-__device__ __noinline__ void penalised_survivor(float raw, int gidx, float thr, bool incl, float inv_temp, float pen) {
+__device__ __forceinline__ void append_binned(Cand* buf, Ctl* ctl, float v, int gidx) {
+    int slot = atomicAdd(&ctl->cnt, 1);
+    if (slot < S::CAP) {
+        Cand e;
+        e.key = f2key(v);
+        e.idx = (uint32_t)gidx;
+        buf[slot] = e;
+        uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
+        const float2 bs = *reinterpret_cast<const float2*>(&ctl->hbase);  // base, scale
+        atomicAdd(&hist[hist_bin(v, bs.x, bs.y)], 1u);
+    }
+}
+
+// Called by one whole warp: the key of the smallest value of the highest bin at which the counts
+// from the top reach `need`, or 0 when they never do or do so only in the lowest bin.  Every
+// counted value whose bin is that one or higher has a key of at least the returned one.
+template <class S>
+__device__ __noinline__ uint32_t hist_threshold(int need_) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const volatile uint32_t* hist = reinterpret_cast<const volatile uint32_t*>(smem_raw + 8 * (size_t)S::CAP);
+    const Ctl* ctl = reinterpret_cast<const Ctl*>(smem_raw + S::CTL_OFF);
+    static_assert(HBINS == 256, "a lane owns eight bins");
+    const int lane = threadIdx.x & 31;
+    const uint32_t need = (uint32_t)need_;
+    uint32_t c[8];
+    uint32_t tot = 0;
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        c[b] = hist[lane * 8 + b];
+        tot += c[b];
+    }
+    uint32_t above = tot;  // inclusive suffix sum over lanes >= me
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        uint32_t y = __shfl_down_sync(0xffffffffu, above, o);
+        if (lane + o < 32) above += y;
+    }
+    above -= tot;  // entries in bins owned by higher lanes
+    uint32_t key = 0u;
+    if (above < need && need <= above + tot) {
+        int bin = 0;
+        uint32_t run = above;
+#pragma unroll
+        for (int b = 7; b >= 0; b--) {
+            if (run < need && need <= run + c[b]) bin = lane * 8 + b;
+            run += c[b];
+        }
+        const float base = ctl->hbase, scale = ctl->hscale;
+        if (bin > 0 && scale > 0.0f) {
+            // A value of a lower bin, as close to the edge as a few steps get: whatever is counted in
+            // `bin` or above is larger (the map is non-decreasing), so the next key up is reached by all.
+            float t = __fadd_rn(base, __fmul_rn((float)bin, ctl->hwidth));
+            uint32_t tk = f2key(t);
+            int tries = 0;
+            while (hist_bin(key2f(tk), base, scale) >= bin && tries < 16) {
+                tk -= 1u;
+                tries++;
+            }
+            if (tries < 16) key = tk + 1u;
+        }
+    }
+    const uint32_t who = __ballot_sync(0xffffffffu, key != 0u);
+    return who ? __shfl_sync(0xffffffffu, key, __ffs(who) - 1) : 0u;
+}
+
+// One column whose RAW value reached the filter.  The penalty only ever lowers a logit
+// (l/p < l for l > 0, l*p < l for l < 0, p > 1) and post-processing is filtered through a raw bound
+// (post_raw_bound), so filtering raw values first is conservative: only here, on the rare
+// survivor, are the exact value computed (a few hundred instructions with post-processing: two
+// divides, fastExp or tanhf), the bitmap consulted, the penalty applied and the filter repeated
+// -- against the threshold of this moment, which may have risen since the caller read its own.
+// Out of line and once per kernel: inlined wherever a survivor can turn up, this code made the
+// streaming loop outgrow the instruction cache (as many stalls waiting for instructions as at
+// barriers).  What it needs of the row sits in the control block; the candidate buffer, the
+// control block and the bitmap are at fixed offsets of the CTA's shared memory.
+template <class S, bool POST>
+__device__ __noinline__ void survivor(float raw, int e) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Cand* buf = reinterpret_cast<Cand*>(smem_raw);
-    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + 8 * (size_t)S::CAP + 4 * 256);
-    const float v = __fmul_rn(penalise(raw, pen), inv_temp);
-    if (incl ? v >= thr : v > thr) append<S>(buf, ctl, v, gidx);
-}
-template <class S, bool INCL>
-__device__ __forceinline__ void consider(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, float v, int e, float thr) {
-    if (c.pen_bitmap && bm_test(c.bm, e)) {
-        penalised_survivor<S>(raw, e + c.voff, thr, INCL, c.inv_temp, c.pen);
-        return;
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + S::CTL_OFF);
+    const uint32_t* bm = reinterpret_cast<const uint32_t*>(smem_raw + S::SMEM_FIXED);
+    float l = raw;
+    if (POST) {
+        const Post post = {ctl->post_mode, ctl->post_scale, ctl->post_cap};
+        l = post_logit(l, post);
     }
-    append<S>(buf, ctl, v, e + c.voff);
+    if (ctl->pen_on && bm_test(bm, e)) l = penalise(l, ctl->pen);
+    const float v = __fmul_rn(l, ctl->inv_temp);
+    if (v >= *reinterpret_cast<const volatile float*>(&ctl->thr)) append_binned<S>(buf, ctl, v, e + ctl->voff);
 }
 
-// The largest scaled value of one complete vector, with the penalty applied to the flagged
-// columns: used for the first region only, whose thread-maxima seed the threshold.
-template <typename T>
-__device__ __forceinline__ float vec_max_penalised(const uint4& rawv, int vec, const RowCtx& c) {
-    constexpr int VEC = Elem<T>::VEC;
-    float raw[VEC];
-    Elem<T>::widen(rawv, raw);
-    const int e0 = vec * VEC - c.mis;
-    float m = __uint_as_float(0xff800000u);
-#pragma unroll
-    for (int j = 0; j < VEC; j++) {
-        float l = raw[j];
-        if (c.pen_bitmap && bm_test(c.bm, e0 + j)) l = penalise(l, c.pen);
-        m = fmaxf(m, __fmul_rn(l, c.inv_temp));
+// In the streaming loop a lane that finds a survivor only sets it aside -- raw value and column,
+// two shared-memory operations -- in its warp's staging area; the warp works its staged survivors
+// off together at the end of a region (flush_staged: one lane each, everything above in lock step,
+// one reservation in the candidate buffer for all of them).  A lane that finds the area full takes
+// the survivor through the code above at once.
+template <class S, bool POST>
+__device__ __forceinline__ void stage(float raw, int e) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    int* wcnt = reinterpret_cast<int*>(smem_raw + S::WCNT_OFF);
+    const int warp = threadIdx.x >> 5;
+    const int slot = atomicAdd(&wcnt[warp], 1);
+    if (slot < S::STG)
+        reinterpret_cast<uint2*>(smem_raw + S::STG_OFF)[warp * S::STG + slot] = make_uint2(__float_as_uint(raw), (uint32_t)e);
+    else
+        survivor<S, POST>(raw, e);
+}
+
+// Called by one whole warp between two regions.
+template <class S, bool POST>
+__device__ __noinline__ void flush_staged() {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + S::CTL_OFF);
+    const uint32_t* bm = reinterpret_cast<const uint32_t*>(smem_raw + S::SMEM_FIXED);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int* wc = reinterpret_cast<int*>(smem_raw + S::WCNT_OFF) + warp;
+    __syncwarp();
+    const int n = min(*reinterpret_cast<volatile int*>(wc), S::STG);
+    bool pass = false;
+    float v = 0.0f;
+    int e = 0;
+    if (lane < n) {
+        const uint2 st = reinterpret_cast<const uint2*>(smem_raw + S::STG_OFF)[warp * S::STG + lane];
+        e = (int)st.y;
+        float l = __uint_as_float(st.x);
+        if (POST) {
+            const Post post = {ctl->post_mode, ctl->post_scale, ctl->post_cap};
+            l = post_logit(l, post);
+        }
+        if (ctl->pen_on && bm_test(bm, e)) l = penalise(l, ctl->pen);
+        v = __fmul_rn(l, ctl->inv_temp);
+        pass = v >= *reinterpret_cast<const volatile float*>(&ctl->thr);
     }
-    return m;
+    const uint32_t m = __ballot_sync(0xffffffffu, pass);
+    if (m) {
+        int base = 0;
+        if (lane == 0) base = atomicAdd(&ctl->cnt, __popc(m));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        const int slot = base + __popc(m & ((1u << lane) - 1u));
+        if (pass && slot < S::CAP) {
+            Cand c;
+            c.key = f2key(v);
+            c.idx = (uint32_t)(e + ctl->voff);
+            buf[slot] = c;
+            const float2 bs = *reinterpret_cast<const float2*>(&ctl->hbase);
+            atomicAdd(&hist[hist_bin(v, bs.x, bs.y)], 1u);
+        }
+    }
+    __syncwarp();
+    if (lane == 0) *wc = 0;
+    __syncwarp();
 }
 
-// The largest scaled value of one complete vector (no penalty: raw values bound the true ones).
-template <typename T>
-__device__ __forceinline__ float vec_max_scaled(const uint4& rawv, float inv_temp) {
-    constexpr int VEC = Elem<T>::VEC;
-    float raw[VEC];
-    Elem<T>::widen(rawv, raw);
-    float m = __fmul_rn(raw[0], inv_temp);
-#pragma unroll
-    for (int j = 1; j < VEC; j++) m = fmaxf(m, __fmul_rn(raw[j], inv_temp));
-    return m;
-}
-
-// One complete 16-byte vector that may hold a survivor.  Survivors are walked one at a time
-// (NaN never passes a compare), so the slow code exists once per call site.
-template <class S, typename T, bool INCL>
-__device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const RowCtx& c, float thr, Cand* buf,
-                                           Ctl* ctl) {
+// One complete 16-byte vector that may hold a survivor: the columns whose raw value reaches `rawthr`
+// (for a batch without post-processing: whose scaled value reaches `thr`) are walked one at a time
+// (NaN never passes a compare).
+template <class S, typename T, bool POST>
+__device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, int mis, float inv_temp, float thr, float rawthr) {
     constexpr int VEC = Elem<T>::VEC;
     float raw[VEC];
     Elem<T>::widen(rawv, raw);
     uint32_t pass = 0;
 #pragma unroll
     for (int j = 0; j < VEC; j++) {
-        float x = __fmul_rn(raw[j], c.inv_temp);
-        pass |= (INCL ? x >= thr : x > thr) ? (1u << j) : 0u;
+        const bool in = POST ? raw[j] >= rawthr : __fmul_rn(raw[j], inv_temp) >= thr;
+        pass |= in ? (1u << j) : 0u;
     }
-    const int e0 = vec * VEC - c.mis;
+    const int e0 = vec * VEC - mis;
     while (pass) {
         const int j = __ffs(pass) - 1;
         pass &= pass - 1;
         float r = raw[0];
 #pragma unroll
         for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
-        consider<S, INCL>(buf, ctl, c, r, __fmul_rn(r, c.inv_temp), e0 + j, thr);
+        stage<S, POST>(r, e0 + j);
     }
-}
-
-// The same three steps for a batch with post-processing: the hot test runs on the raw logits
-// against a raw bound (post_raw_bound), and only a column that passes it pays for the exact value.
-// The exact value of a survivor is a few hundred instructions (two divides, fastExp or tanhf).
-// Inlined at every place a survivor can turn up it made the streaming loop too large for the
-// instruction cache (measured: as many stalls waiting for instructions as at barriers), so it
-// exists once per kernel, out of line, with everything it needs passed by value; the candidate
-// buffer and the control block sit at fixed offsets of the CTA's shared memory.
-template <class S>
-__device__ __noinline__ void post_survivor(float raw, int e, float thr, bool incl, float inv_temp, float pen,
-                                           int voff, int mode, float scale, float cap) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
-    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + 8 * (size_t)S::CAP + 4 * 256);
-    const Post post = {mode, scale, cap};
-    float l = post_logit(raw, post);
-    if (pen != 0.0f) l = penalise(l, pen);  // 0: this column carries no penalty
-    const float v = __fmul_rn(l, inv_temp);
-    if (incl ? v >= thr : v > thr) append<S>(buf, ctl, v, e + voff);
-}
-template <class S, bool INCL>
-__device__ __forceinline__ void consider_post(Cand* buf, Ctl* ctl, const RowCtx& c, const Post& post, float raw,
-                                              int e, float thr) {
-    post_survivor<S>(raw, e, thr, INCL, c.inv_temp, (c.pen_bitmap && bm_test(c.bm, e)) ? c.pen : 0.0f, c.voff,
-                     post.mode, post.scale, post.cap);
 }
 
 // The largest raw logit of one complete vector.
@@ -419,24 +532,49 @@ __device__ __forceinline__ float vec_max_raw<bf16_t>(const uint4& rawv) {
     return fmaxf(__low2float(m2), __high2float(m2));
 }
 
-template <class S, typename T, bool INCL>
-__device__ __forceinline__ void filter_vec_post(const uint4& rawv, int vec, const RowCtx& c, const Post& post,
-                                                float rthr, float thr, Cand* buf, Ctl* ctl) {
-    constexpr int VEC = Elem<T>::VEC;
-    float raw[VEC];
-    Elem<T>::widen(rawv, raw);
-    uint32_t pass = 0;
-#pragma unroll
-    for (int j = 0; j < VEC; j++) pass |= (raw[j] >= rthr) ? (1u << j) : 0u;
-    const int e0 = vec * VEC - c.mis;
-    while (pass) {
-        const int j = __ffs(pass) - 1;
-        pass &= pass - 1;
-        float r = raw[0];
-#pragma unroll
-        for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
-        consider_post<S, INCL>(buf, ctl, c, post, r, e0 + j, thr);
-    }
+// The streaming loop's one test per thread and region is on the largest raw logit of the region's
+// U vectors.  It is built from one partial maximum per vector, which the rarer path that follows a
+// passed test finishes into that vector's own maximum (one more instruction) instead of starting over.
+// float32: three-input maxima (sm_100) -- eight instructions for sixteen values; the partial is the
+// maximum of the first three lanes of the vector.
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
 }
+template <typename T>
+struct VecPart;
+template <>
+struct VecPart<float> {
+    typedef float part_t;
+    __device__ static __forceinline__ part_t part(const uint4& v) {
+        return max3f(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z));
+    }
+    __device__ static __forceinline__ float finish(part_t p, const uint4& v) { return fmaxf(p, __uint_as_float(v.w)); }
+    template <int U>
+    __device__ static __forceinline__ float region(const part_t (&p)[U], const uint4 (&v)[U]) {
+        float m = p[0];
+#pragma unroll
+        for (int u = 1; u < U; u++) m = max3f(m, __uint_as_float(v[u - 1].w), p[u]);
+        return fmaxf(m, __uint_as_float(v[U - 1].w));
+    }
+};
+// bfloat16: packed two-wide maxima; the partial is the vector's maximum still packed as a pair.
+template <>
+struct VecPart<bf16_t> {
+    typedef __nv_bfloat162 part_t;
+    __device__ static __forceinline__ part_t part(const uint4& v) {
+        return __hmax2(__hmax2(*reinterpret_cast<const __nv_bfloat162*>(&v.x), *reinterpret_cast<const __nv_bfloat162*>(&v.y)),
+                       __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&v.z), *reinterpret_cast<const __nv_bfloat162*>(&v.w)));
+    }
+    __device__ static __forceinline__ float finish(part_t p, const uint4&) { return fmaxf(__low2float(p), __high2float(p)); }
+    template <int U>
+    __device__ static __forceinline__ float region(const part_t (&p)[U], const uint4 (&)[U]) {
+        part_t m = p[0];
+#pragma unroll
+        for (int u = 1; u < U; u++) m = __hmax2(m, p[u]);
+        return fmaxf(__low2float(m), __high2float(m));
+    }
+};
 
 }  // namespace

@@ -271,7 +271,7 @@ int launch_merge(KArgs& a, cudaStream_t stream, bool dependent = false) {
     const long long held = (long long)a.parts * std::min(a.part_cap, a.max_top_k);
     if (a.max_top_k <= ShapeK256::KCAP && held <= ShapeK256::CAP / 2)
         return launch_merge_as<ShapeK256>(a, stream, dependent);
-    return launch_merge_as<ShapeK1024>(a, stream, dependent);
+    return launch_merge_as<ShapeMerge>(a, stream, dependent);
 }
 
 // Long shortlists: wide_hist_kernel settles the rows, wide_rows_kernel behind it takes the few it

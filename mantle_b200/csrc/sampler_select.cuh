@@ -205,6 +205,34 @@ __device__ __forceinline__ uint32_t rank_select(Cand* buf, Ctl* ctl, int n, int 
     return (uint32_t)ctl->sel_bin;
 }
 
+// The counting select for NT < n <= 2 * NT: two entries per thread, one read of the buffer for both.
+template <class S>
+__device__ __forceinline__ uint32_t rank_select2(Cand* buf, Ctl* ctl, int n, int k, int tid, bool* have_kth) {
+    static_assert(S::NT == RANK_MAX, "every thread holds a first entry");
+    const Cand me0 = buf[tid];
+    Cand me1;
+    me1.key = 0;
+    me1.idx = 0xffffffffu;
+    const bool two = tid + S::NT < n;
+    if (two) me1 = buf[tid + S::NT];
+    int r0 = 0, r1 = 0;
+    for (int j = 0; j < n; j++) {
+        const Cand o = buf[j];
+        r0 += ((o.key > me0.key) | ((o.key == me0.key) & (o.idx < me0.idx))) ? 1 : 0;
+        r1 += ((o.key > me1.key) | ((o.key == me1.key) & (o.idx < me1.idx))) ? 1 : 0;
+    }
+    if (!two) r1 = 0x7fffffff;
+    __syncthreads();
+    if (r0 < k) buf[r0] = me0;
+    if (r1 < k) buf[r1] = me1;
+    if (r0 == k - 1) ctl->sel_bin = (int)me0.key;
+    if (r1 == k - 1) ctl->sel_bin = (int)me1.key;
+    if (tid == 0) ctl->cnt = min(n, k);
+    __syncthreads();
+    *have_kth = n >= k;
+    return (uint32_t)ctl->sel_bin;
+}
+
 // Cut the buffer to its k best entries, by counting when it is small and by radix select
 // otherwise.  Called by every thread with the buffer quiescent.
 template <class S>
@@ -213,9 +241,109 @@ __device__ __forceinline__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* 
     __syncthreads();
     const int n = live_count(ctl);
     __syncthreads();
-    if (ordered) *ordered = n <= RANK_MAX;  // the counting select leaves its survivors in order
+    constexpr int RANK2 = S::NT == RANK_MAX ? 2 * RANK_MAX : RANK_MAX;
+    if (ordered) *ordered = n <= RANK2;  // the counting select leaves its survivors in order
     if (n <= RANK_MAX) return rank_select(buf, ctl, n, k, tid, have_kth);
+    if constexpr (S::NT == RANK_MAX) {
+        if (n <= RANK2) return rank_select2<S>(buf, ctl, n, k, tid, have_kth);
+    }
     return select_topk<S>(buf, ctl, hist, k, tid, have_kth);
+}
+
+// ---------------------------------------------------------------------------------------
+// The running histogram's side of the buffer (hist_bin, append_binned, hist_threshold).
+
+// Zeroes the histogram and counts the first n entries of the buffer again.  Every thread; the
+// buffer quiescent; ends with a barrier.
+template <class S>
+__device__ __forceinline__ void hist_rebuild(const Cand* buf, const Ctl* ctl, uint32_t* hist, int n, int tid) {
+    for (int i = tid; i < HBINS; i += S::NT) hist[i] = 0u;
+    __syncthreads();
+    const float base = ctl->hbase, scale = ctl->hscale;
+    for (int i = tid; i < n; i += S::NT) atomicAdd(&hist[hist_bin(key2f(buf[i].key), base, scale)], 1u);
+    __syncthreads();
+}
+
+// Drops the entries below the histogram's threshold.  Called by every thread behind a barrier
+// that follows the last append; returns true if the buffer has overflowed (the row is redone on
+// the careful path).  With `rebuild` the histogram is counted again from what is left, so that
+// it never counts an entry the buffer no longer holds.
+template <class S>
+__device__ __forceinline__ bool hist_compact(Cand* buf, Ctl* ctl, uint32_t* hist, int tid, bool rebuild) {
+    constexpr int NT = S::NT, EPT = S::EPT;
+    const int n = live_count(ctl);
+    if (n > S::CAP) return true;
+    if (tid < 32) {
+        const uint32_t key = hist_threshold<S>(ctl->k);
+        if (tid == 0 && key > ctl->thr_key) {
+            ctl->thr_key = key;
+            ctl->thr = key2f(key);
+        }
+    }
+    __syncthreads();
+    const uint32_t tk = ctl->thr_key;
+    Cand mine[EPT];
+    uint32_t keep = 0;
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        const int i = tid + j * NT;
+        if (i < n) {
+            mine[j] = buf[i];
+            if (mine[j].key >= tk) keep |= 1u << j;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) ctl->cnt = 0;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        if ((keep >> j) & 1u) {
+            const int slot = atomicAdd(&ctl->cnt, 1);
+            buf[slot] = mine[j];
+        }
+    }
+    __syncthreads();
+    if (tid == 0) ctl->walked = live_count(ctl);
+    if (rebuild) hist_rebuild<S>(buf, ctl, hist, live_count(ctl), tid);
+    return false;
+}
+
+// A meeting of the streaming loop at which the buffer holds more than FORCE entries: compact it by
+// the histogram's threshold and, if that does not free it (values tied in their thousands, bins
+// too coarse for this row), cut it exactly and lay the bins over what is left.  Every warp is
+// between two regions here, so every buffered entry has a lower index than every column still to
+// come, and a column that only EQUALS the k-th key of an exact cut can no longer enter: the
+// threshold becomes the next key above it.  Returns true if the buffer has overflowed.
+template <class S>
+__device__ __noinline__ bool forced_cut(int tid) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(buf + S::CAP);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + S::CTL_OFF);
+    if (hist_compact<S>(buf, ctl, hist, tid, true)) return true;
+    if (live_count(ctl) <= S::FORCE) return false;
+    bool have;
+    if (tid == 0) ctl->kmax = 0u;
+    const uint32_t kth = refresh_topk<S>(buf, ctl, hist, ctl->k, tid, &have);
+    const int left = live_count(ctl);
+    uint32_t top_key = 0u;
+    for (int i = tid; i < left; i += S::NT) top_key = max(top_key, buf[i].key);
+    atomicMax(&ctl->kmax, top_key);
+    __syncthreads();
+    if (tid == 0 && have) {
+        // the bins now span what the cut left: its k-th value to its largest
+        ctl->thr_key = max(ctl->thr_key, kth + 1u);
+        ctl->thr = key2f(ctl->thr_key);
+        const float base = key2f(kth), top = key2f(ctl->kmax);
+        const bool ok = top > base && top - base < 3.0e38f;
+        ctl->hbase = base;
+        ctl->htop = top;
+        ctl->hscale = ok ? (float)HBINS / (top - base) : 0.0f;
+        ctl->hwidth = ok ? (top - base) / (float)HBINS : 0.0f;
+    }
+    __syncthreads();
+    hist_rebuild<S>(buf, ctl, hist, live_count(ctl), tid);
+    return false;
 }
 
 // a precedes b in the shortlist order (key descending, index ascending).  By value and without
