@@ -447,6 +447,7 @@ __device__ __noinline__ void flush_staged() {
     int* wc = reinterpret_cast<int*>(smem_raw + S::WCNT_OFF) + warp;
     __syncwarp();
     const int n = min(*reinterpret_cast<volatile int*>(wc), S::STG);
+    if (n == 0) return;
     bool pass = false;
     float v = 0.0f;
     int e = 0;

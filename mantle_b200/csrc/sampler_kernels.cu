@@ -152,7 +152,8 @@ int ensure_smem(K kern, size_t smem, std::atomic<int>* granted) {
     return 0;
 }
 
-bool small_shape(int max_top_k) { return max_top_k <= ShapeK256::KCAP; }
+// (from 225 entries on the seed of the small shape -- one value per thread -- admits a third of region 0)
+bool small_shape(int max_top_k) { return max_top_k <= 224; }
 
 int choose_splits(const MantleSampleBatch* b) {
     if (b->max_top_k > KMAX) return 1;  // long shortlists: one CTA per row, no merge

@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             // warp split over two of its own meeting points does not return)
             __syncwarp();
             const int staged = __shfl_sync(0xffffffffu, wcnt[warp], 0);
-            if (staged >= 8 || r < 8 || (r & (r - 1)) == 0) flush_staged<S, POST>();
+            if (staged >= 16 || r < 8 || (r & (r - 1)) == 0) flush_staged<S, POST>();
             if ((r & (NWARP - 1)) == warp) {
                 const int n = live_count(ctl);
                 const int fresh_entries = __shfl_sync(0xffffffffu, n - ctl->walked, 0);
@@ -209,13 +209,12 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
             // (post-processing up to its slack, penalty, temperature) is non-decreasing, and a
             // column's value is at least what it would be with the penalty, so the image of a raw
             // logit that k columns reach is a value that k columns reach -- no bitmap lookups here.
-            float lo, top;  // the range the seeding histogram is laid over
-            float tmax = __uint_as_float(0xff800000u);
+            float t0, h0;  // raw: what k columns of the region reach, and what about half as many reach
             if constexpr (!SEED_HIST) {
-                // Up to 32 * NWARP entries: the histogram counts the threads' maxima.  Its range comes
-                // from a sort of each warp's maxima: from the smallest of the warps' j-th largest
-                // (itself a valid seed: NWARP * j >= k columns reach it) to the largest of the warps'
-                // second largest, so that a few outliers do not stretch the bins.
+                // Up to 32 * NWARP entries: from a sort of each warp's thread maxima.  NWARP * j >= k
+                // columns reach the smallest of the warps' j-th largest; the largest of their
+                // (j / 2)-th largest spans the bins, so that a few outliers do not stretch them.
+                float tmax = __uint_as_float(0xff800000u);
 #pragma unroll
                 for (int u = 0; u < U; u++)
                     if (v0 + u * NT < b0) tmax = fmaxf(tmax, vec_max_raw<T>(ra[u]));
@@ -232,24 +231,23 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                 }
                 const int j = (k + NWARP - 1) / NWARP;
                 const float wj = __shfl_sync(0xffffffffu, x, j - 1);
-                const float w2 = __shfl_sync(0xffffffffu, x, 1);
+                const float wh = __shfl_sync(0xffffffffu, x, (j - 1) >> 1);
                 if (lane == 0) {
                     ctl->warpv[warp] = wj;
-                    ctl->warpk_min[warp] = __float_as_uint(w2);
+                    ctl->warpk_min[warp] = __float_as_uint(wh);
                 }
                 __syncthreads();
-                lo = ctl->warpv[0];
-                top = __uint_as_float(ctl->warpk_min[0]);
+                t0 = ctl->warpv[0];
+                h0 = __uint_as_float(ctl->warpk_min[0]);
 #pragma unroll
                 for (int w = 1; w < NWARP; w++) {
-                    lo = fminf(lo, ctl->warpv[w]);
-                    top = fmaxf(top, __uint_as_float(ctl->warpk_min[w]));
+                    t0 = fminf(t0, ctl->warpv[w]);
+                    h0 = fmaxf(h0, __uint_as_float(ctl->warpk_min[w]));
                 }
             } else {
-                // Longer shortlists: the histogram counts every raw value of region 0, over the
-                // region's own range.
-                lo = __uint_as_float(0x7f800000u);
-                top = __uint_as_float(0xff800000u);
+                // Longer shortlists: every raw value of region 0 is counted in the histogram, laid
+                // over the region's own range, and every warp walks it for itself.
+                float lo = __uint_as_float(0x7f800000u), top = __uint_as_float(0xff800000u);
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     if (v0 + u * NT < b0) {
@@ -279,16 +277,12 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                     lo = fminf(lo, __uint_as_float(ctl->warpk_min[w]));
                     top = fmaxf(top, ctl->warpv[w]);
                 }
-            }
-            const float sc = (top > lo && top - lo < 3.0e38f) ? (float)HBINS / (top - lo) : 0.0f;
-            if (tid == 0) {
-                ctl->hbase = lo;
-                ctl->hscale = sc;
-                ctl->hwidth = sc > 0.0f ? (top - lo) / (float)HBINS : 0.0f;
-            }
-            if constexpr (!SEED_HIST) {
-                if (tmax >= lo) atomicAdd(&hist[hist_bin(tmax, lo, sc)], 1u);
-            } else {
+                const float sc = (top > lo && top - lo < 3.0e38f) ? (float)HBINS / (top - lo) : 0.0f;
+                if (tid == 0) {
+                    ctl->hbase = lo;
+                    ctl->hscale = sc;
+                    ctl->hwidth = sc > 0.0f ? (top - lo) / (float)HBINS : 0.0f;
+                }
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     if (v0 + u * NT < b0) {
@@ -299,23 +293,15 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                             if (raw[i] >= lo) atomicAdd(&hist[hist_bin(raw[i], lo, sc)], 1u);
                     }
                 }
-            }
-            __syncthreads();
-            if (warp == 0) {
-                // what k of the counted values reach, and what half as many reach
+                __syncthreads();
                 const uint32_t kk = hist_threshold<S>(k);
                 const uint32_t kh = hist_threshold<S>((k + 1) >> 1);
-                if (lane == 0) {
-                    ctl->warpk_max[0] = kk;
-                    ctl->warpk_max[1] = kh;
-                }
+                // (with fewer than k columns in the region there is no seed)
+                t0 = kk ? key2f(kk) : __uint_as_float(0xff800000u);
+                h0 = kh ? key2f(kh) : top;
+                __syncthreads();
+                for (int i = tid; i < HBINS; i += NT) hist[i] = 0u;
             }
-            __syncthreads();
-            const uint32_t kk = ctl->warpk_max[0], kh = ctl->warpk_max[1];
-            // (with fewer than k columns in the region the seed stays what it was, -inf from an empty lane)
-            float t0 = kk ? key2f(kk) : (SEED_HIST ? __uint_as_float(0xff800000u) : lo);
-            float h0 = kh ? key2f(kh) : top;
-            for (int i = tid; i < HBINS; i += NT) hist[i] = 0u;
             if (POST) {
                 t0 = post_seed_logit(t0, POSTP);
                 h0 = post_seed_logit(h0, POSTP);
@@ -327,7 +313,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                 // The bins of the running histogram start at the seed and span twelve times the
                 // distance to the value half as many columns reach: the k-th value of the whole row
                 // lies a few such distances up, and whatever lies beyond the span shares the top bin.
-                const float span = __fmul_rn(12.0f, __fsub_rn(h0, t0));
+                const float span = __fmul_rn(SEED_HIST ? 12.0f : 8.0f, __fsub_rn(h0, t0));
                 const bool ok = span > 0.0f && span < 3.0e38f;
                 ctl->thr_key = f2key(t0);
                 ctl->thr = t0;
@@ -344,21 +330,21 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
                 if (v0 + u * NT < b0) filter_vec<S, T, POST>(ra[u], v0 + u * NT, c.mis, c.inv_temp, thr, rthr);
             flush_staged<S, POST>();
         }
-        // the first meeting: every append of region 0 is counted before the threshold is read
+        // the first meeting: every append of region 0 is counted before the threshold is read; every
+        // warp walks the histogram for itself
         __syncthreads();
-        if (live_count(ctl) > CAP) careful = true;
-        else if (warp == 0) {
+        if (live_count(ctl) > CAP) {
+            careful = true;
+        } else {
             const uint32_t key = hist_threshold<S>(k);
-            if (lane == 0) {
+            if (key > f2key(thr)) thr = key2f(key);
+            if (POST) rthr = post_raw_bound(thr, c.inv_temp, POSTP);
+            if (tid == 0) {
                 ctl->walked = live_count(ctl);
-                if (key > ctl->thr_key) {
-                    ctl->thr_key = key;
-                    ctl->thr = key2f(key);
-                }
+                ctl->thr_key = f2key(thr);
+                ctl->thr = thr;
             }
         }
-        __syncthreads();
-        fresh();
 
         // -- regions 1.. : two register sets, each refilled while the other is filtered --
         int r = 1;  // rb holds region r
@@ -404,7 +390,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         }
         __syncthreads();
         // what the histogram's threshold leaves is a few entries more than k: the exact cut's work
-        if (live_count(ctl) > RANK_MAX) careful = hist_compact<S>(buf, ctl, hist, tid, false);
+        if (live_count(ctl) > k + 32) careful = hist_compact<S>(buf, ctl, hist, tid, false);
         else __syncthreads();
     }
 
