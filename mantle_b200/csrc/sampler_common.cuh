@@ -41,7 +41,6 @@ struct Shape {
 using ShapeK256 = Shape<256, 4, 2048, 256, 4>;    // top_k <= 256: 16 KB candidate buffer, four CTAs per SM
 using ShapeK1024 = Shape<256, 4, 4096, KMAX, 4>;  // top_k <= 1024: 32 KB candidate buffer
 using ShapeMerge = Shape<512, 4, 4096, KMAX, 1>;  // the merge kernel where the parts hold more than ShapeK256 takes
-constexpr int VOTE_EVERY = 2;  // regions between two "does the buffer need a cut" votes
 constexpr int MAX_NWARP = 32;
 constexpr int MERGE_CAP = ShapeMerge::CAP;
 
@@ -376,16 +375,11 @@ __device__ __noinline__ uint32_t hist_threshold(int need_) {
         }
         const float base = ctl->hbase, scale = ctl->hscale;
         if (bin > 0 && scale > 0.0f) {
-            // A value of a lower bin, as close to the edge as a few steps get: whatever is counted in
-            // `bin` or above is larger (the map is non-decreasing), so the next key up is reached by all.
-            float t = __fadd_rn(base, __fmul_rn((float)bin, ctl->hwidth));
-            uint32_t tk = f2key(t);
-            int tries = 0;
-            while (hist_bin(key2f(tk), base, scale) >= bin && tries < 16) {
-                tk -= 1u;
-                tries++;
-            }
-            if (tries < 16) key = tk + 1u;
+            // A value half a bin below the edge, which the bin function puts into a lower bin (checked):
+            // whatever is counted in `bin` or above is larger (the map is non-decreasing), so the next
+            // key up is reached by all of it.
+            const float t = __fadd_rn(base, __fmul_rn((float)bin - 0.5f, ctl->hwidth));
+            if (hist_bin(t, base, scale) < bin) key = f2key(t) + 1u;
         }
     }
     const uint32_t who = __ballot_sync(0xffffffffu, key != 0u);

@@ -50,6 +50,7 @@
 #include "sampler_async.cuh"
 #include "sampler_rows.cuh"
 #include "scan_rows_ldg.cuh"
+#include "scan_rows_hist.cuh"
 #include "wide_rows.cuh"
 #include "wide_rows_fast.cuh"
 #include "merge_parts.cuh"
@@ -215,33 +216,35 @@ void fill_args(KArgs& a, const MantleSampleBatch* b) {
 #endif
 }
 
-template <class S, typename T, int MODE, bool POST>
+// CUT: the kernel that cuts its buffer exactly (short shortlists); else the one with the running histogram.
+template <class S, typename T, int MODE, bool POST, bool CUT>
 int launch_scan_as(const KArgs& a, cudaStream_t stream) {
     static std::atomic<int> granted[kMaxDevices];
     const size_t smem = S::SMEM_FIXED + bitmap_words(a.vocab) * sizeof(uint32_t);
     const long long items = (long long)a.rows * a.splits;
     if (items > 0x7fffffffLL) return kInvalid;
-    auto kern = scan_rows_ldg_kernel<S, T, MODE, POST>;
+    auto kern = CUT ? scan_rows_ldg_kernel<S, T, MODE, POST> : scan_rows_hist_kernel<S, T, MODE, POST>;
     const int rc = ensure_smem(kern, smem, granted);
     if (rc) return rc;
     kern<<<(int)items, S::NT, smem, stream>>>(a);
     return (int)cudaGetLastError();
 }
 
-template <class S, int MODE>
+template <class S, int MODE, bool CUT>
 int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
     if (a.post.mode)
-        return dtype == MANTLE_DTYPE_F32 ? launch_scan_as<S, float, MODE, true>(a, stream)
-                                         : launch_scan_as<S, bf16_t, MODE, true>(a, stream);
-    return dtype == MANTLE_DTYPE_F32 ? launch_scan_as<S, float, MODE, false>(a, stream)
-                                     : launch_scan_as<S, bf16_t, MODE, false>(a, stream);
+        return dtype == MANTLE_DTYPE_F32 ? launch_scan_as<S, float, MODE, true, CUT>(a, stream)
+                                         : launch_scan_as<S, bf16_t, MODE, true, CUT>(a, stream);
+    return dtype == MANTLE_DTYPE_F32 ? launch_scan_as<S, float, MODE, false, CUT>(a, stream)
+                                     : launch_scan_as<S, bf16_t, MODE, false, CUT>(a, stream);
 }
 
-// The streaming kernel in the shape that serves the batch's longest shortlist.
+// The streaming kernel, and its shape, that serve the batch's longest shortlist.
 template <int MODE>
 int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
-    if (small_shape(a.max_top_k)) return launch_scan_shape<ShapeK256, MODE>(a, dtype, stream);
-    return launch_scan_shape<ShapeK1024, MODE>(a, dtype, stream);
+    if (a.max_top_k <= CUT_KMAX) return launch_scan_shape<ShapeK256, MODE, true>(a, dtype, stream);
+    if (small_shape(a.max_top_k)) return launch_scan_shape<ShapeK256, MODE, false>(a, dtype, stream);
+    return launch_scan_shape<ShapeK1024, MODE, false>(a, dtype, stream);
 }
 
 // `dependent`: the merge directly follows, on the same stream, the kernel that writes its parts;
@@ -334,7 +337,8 @@ extern "C" int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* spli
 
 extern "C" const char* mantleCudaSamplerKernelName(const MantleSampleBatch* batch) {
     if (!batch_ok(batch, true)) return "";
-    return batch->max_top_k > KMAX ? "wide_hist_kernel" : "scan_rows_ldg_kernel";
+    if (batch->max_top_k > KMAX) return "wide_hist_kernel";
+    return batch->max_top_k <= CUT_KMAX ? "scan_rows_ldg_kernel" : "scan_rows_hist_kernel";
 }
 
 extern "C" int mantleCudaSamplerWorkspaceBytes(const MantleSampleBatch* batch, size_t* bytes) {

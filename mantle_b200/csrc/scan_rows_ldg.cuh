@@ -1,9 +1,120 @@
-// scan_rows_ldg_kernel: the streaming pass with plain 16-byte loads; the default kernel.
+// scan_rows_ldg_kernel: the streaming pass for short shortlists (top_k up to CUT_KMAX), with plain
+// 16-byte loads and an exact cut of the candidate buffer whenever it fills.
 // Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
 // translation unit.
 #pragma once
 
 namespace {
+
+// Up to this shortlist length the buffer is cut exactly, by counting, every time it holds half as
+// many entries again: the cuts rank a few dozen entries and give the exact k-th value as the next
+// threshold.  Longer shortlists go to scan_rows_hist_kernel, whose threshold comes from a running
+// histogram and which never ranks more than the final shortlist (measured on 4096 rows of 151 936
+// float32 columns: 0.405 against 0.428 ms at top_k 20, 0.470 against 0.454 ms at 40, 0.721
+// against 0.531 ms at 100).
+constexpr int CUT_KMAX = 32;
+constexpr int VOTE_EVERY = 2;  // regions between two "does the buffer need a cut" votes
+
+namespace cut {
+
+// One column whose scaled RAW value reached the filter.  The penalty only ever lowers a
+// logit (l/p < l for l > 0, l*p < l for l < 0, p > 1), so filtering raw values first is
+// conservative: only here, on the rare survivor, is the bitmap consulted, the penalty
+// applied and the filter repeated on the true value.
+// A survivor that carries a penalty is rarer still (a column of the history window among the few
+// that pass the filter); its divide lives out of line, once per kernel, so that the streaming
+// loop stays small.  The candidate buffer and the control block sit at fixed offsets.
+template <class S>
+__device__ __noinline__ void penalised_survivor(float raw, int gidx, float thr, bool incl, float inv_temp, float pen) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + S::CTL_OFF);
+    const float v = __fmul_rn(penalise(raw, pen), inv_temp);
+    if (incl ? v >= thr : v > thr) append<S>(buf, ctl, v, gidx);
+}
+template <class S, bool INCL>
+__device__ __forceinline__ void consider(Cand* buf, Ctl* ctl, const RowCtx& c, float raw, float v, int e, float thr) {
+    if (c.pen_bitmap && bm_test(c.bm, e)) {
+        penalised_survivor<S>(raw, e + c.voff, thr, INCL, c.inv_temp, c.pen);
+        return;
+    }
+    append<S>(buf, ctl, v, e + c.voff);
+}
+
+// One complete 16-byte vector that may hold a survivor.  Survivors are walked one at a time
+// (NaN never passes a compare), so the slow code exists once per call site.
+template <class S, typename T, bool INCL>
+__device__ __forceinline__ void filter_vec(const uint4& rawv, int vec, const RowCtx& c, float thr, Cand* buf,
+                                           Ctl* ctl) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    uint32_t pass = 0;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) {
+        float x = __fmul_rn(raw[j], c.inv_temp);
+        pass |= (INCL ? x >= thr : x > thr) ? (1u << j) : 0u;
+    }
+    const int e0 = vec * VEC - c.mis;
+    while (pass) {
+        const int j = __ffs(pass) - 1;
+        pass &= pass - 1;
+        float r = raw[0];
+#pragma unroll
+        for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
+        consider<S, INCL>(buf, ctl, c, r, __fmul_rn(r, c.inv_temp), e0 + j, thr);
+    }
+}
+
+// The same three steps for a batch with post-processing: the hot test runs on the raw logits
+// against a raw bound (post_raw_bound), and only a column that passes it pays for the exact value.
+// The exact value of a survivor is a few hundred instructions (two divides, fastExp or tanhf).
+// Inlined at every place a survivor can turn up it made the streaming loop too large for the
+// instruction cache (measured: as many stalls waiting for instructions as at barriers), so it
+// exists once per kernel, out of line, with everything it needs passed by value; the candidate
+// buffer and the control block sit at fixed offsets of the CTA's shared memory.
+template <class S>
+__device__ __noinline__ void post_survivor(float raw, int e, float thr, bool incl, float inv_temp, float pen,
+                                           int voff, int mode, float scale, float cap) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + S::CTL_OFF);
+    const Post post = {mode, scale, cap};
+    float l = post_logit(raw, post);
+    if (pen != 0.0f) l = penalise(l, pen);  // 0: this column carries no penalty
+    const float v = __fmul_rn(l, inv_temp);
+    if (incl ? v >= thr : v > thr) append<S>(buf, ctl, v, e + voff);
+}
+template <class S, bool INCL>
+__device__ __forceinline__ void consider_post(Cand* buf, Ctl* ctl, const RowCtx& c, const Post& post, float raw,
+                                              int e, float thr) {
+    post_survivor<S>(raw, e, thr, INCL, c.inv_temp, (c.pen_bitmap && bm_test(c.bm, e)) ? c.pen : 0.0f, c.voff,
+                     post.mode, post.scale, post.cap);
+}
+
+template <class S, typename T, bool INCL>
+__device__ __forceinline__ void filter_vec_post(const uint4& rawv, int vec, const RowCtx& c, const Post& post,
+                                                float rthr, float thr, Cand* buf, Ctl* ctl) {
+    constexpr int VEC = Elem<T>::VEC;
+    float raw[VEC];
+    Elem<T>::widen(rawv, raw);
+    uint32_t pass = 0;
+#pragma unroll
+    for (int j = 0; j < VEC; j++) pass |= (raw[j] >= rthr) ? (1u << j) : 0u;
+    const int e0 = vec * VEC - c.mis;
+    while (pass) {
+        const int j = __ffs(pass) - 1;
+        pass &= pass - 1;
+        float r = raw[0];
+#pragma unroll
+        for (int q = 1; q < VEC; q++) r = (j == q) ? raw[q] : r;
+        consider_post<S, INCL>(buf, ctl, c, post, r, e0 + j, thr);
+    }
+}
+
+
+}  // namespace cut
+
 
 // ---------------------------------------------------------------------------------------
 // The streaming pass: one CTA per item (row, split), plain 16-byte loads, two register sets per
@@ -55,56 +166,36 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     const int a0 = g.a0, b0 = g.b0, elo = g.elo, ehi = g.ehi;
     constexpr int RV = NT * U;  // vectors per region
     const int nreg = g.nchunks;
-    // shortlists longer than the thread maxima can seed take their seed from a histogram of region 0
-    constexpr bool SEED_HIST = S::KCAP > 32 * NWARP;
-    bool careful = false;
+    bool careful = k > 32 * NWARP;
 
     // The first region's loads go out before anything else: they are in flight while the bitmap is built.
     uint4 ra[U], rb[U];
-    // A region that may reach beyond the item (its last one): every vector tested against the end.
-    auto load_checked = [&](uint4(&dst)[U], int r) {
+    // Only an item's last region can be partial.  Measured alternatives, each with fewer instructions
+    // and each slower: loads that leave a register beyond the item as it is (they wait for its last
+    // reader, 1.6 %), loads without bounds tests for whole regions (2 %), a -inf fill that spares the
+    // masks below (1 %).
+    auto load = [&](uint4(&dst)[U], int r) {
 #pragma unroll
         for (int u = 0; u < U; u++) {
             int v = a0 + r * RV + u * NT + tid;
             dst[u] = v < b0 ? __ldcs(vbase + v) : make_uint4(0, 0, 0, 0);
         }
     };
-    // A region that lies inside the item: U loads at fixed offsets from a pointer that walks the row.
-    const int nwhole = (b0 - a0) / RV;  // regions [0, nwhole) are complete
-    const uint4* q = vbase + a0 + tid + RV;  // this thread's first vector of region 1
-    auto load_whole = [&](uint4(&dst)[U]) {
-#pragma unroll
-        for (int u = 0; u < U; u++) dst[u] = __ldcs(q + u * NT);
-        q += RV;
-    };
-    // The L2 is asked for a region (one request per 128-byte line: a warp's share of a region is U
-    // runs of 512 bytes, lane i asks for line i & 3 of run i >> 2) two regions before its loads are
-    // issued, so that those loads find their lines on the way or already there.
-    const uint4* pf = vbase + a0 + (lane >> 2) * NT + (tid & ~31) + (lane & 3) * 8;  // region 0's line of this lane
-    const bool pf_lane = lane < 4 * U;
-    auto ahead = [&](int r) {  // any region: the line tested against the end
-        if (r < nreg && pf_lane) {
-            const uint4* l = pf + (size_t)r * RV;
-            if (l < vbase + b0) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(l));
+    // `ahead(r)`: ask the L2 for region r (one request per 128-byte line), two regions before its
+    // loads are issued, so that those loads find their lines on the way or already there
+    auto ahead = [&](int r) {
+        // a warp's share of a region is U runs of 512 bytes: lane i asks for line i & 3 of run i >> 2
+        if (r < nreg && lane < 4 * U) {
+            const int v = a0 + r * RV + (lane >> 2) * NT + (tid & ~31) + (lane & 3) * 8;
+            if (v < b0) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(vbase + v));
         }
     };
-    if (nreg > 0) {
-        load_checked(ra, 0);
+    if (!careful && nreg > 0) {
+        load(ra, 0);
         ahead(1);
         ahead(2);
-        ahead(3);
     }
-    if (tid == 0) {
-        ctl->cnt = 0;
-        ctl->k = k;
-        ctl->thr_key = 0u;
-        ctl->thr = __uint_as_float(0xff800000u);
-        ctl->walked = 0;
-        ctl->hbase = ctl->hscale = ctl->htop = ctl->hwidth = 0.0f;  // one bin until region 0 has laid them out
-    }
-    for (int i = tid; i < HBINS; i += NT) hist[i] = 0u;
-    volatile int* wcnt = reinterpret_cast<volatile int*>(smem_raw + S::WCNT_OFF);
-    if (tid < NWARP) wcnt[tid] = 0;
+    if (tid == 0) ctl->cnt = 0;
 
     // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
     const int hl = history_len(a, row);
@@ -113,269 +204,136 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         build_penalty_bitmap_early<NT>(a, row, wp, hl, c.V, c.voff, bm, tid);
         c.pen_bitmap = true;
     }
-    if (tid == 0) {  // what the out-of-line survivor code reads
-        ctl->pen_on = wp.active ? 1 : 0;
-        ctl->inv_temp = c.inv_temp;
-        ctl->pen = c.pen;
-        ctl->voff = c.voff;
-        ctl->post_mode = a.post.mode;
-        ctl->post_scale = a.post.scale;
-        ctl->post_cap = a.post.cap;
-    }
     __syncthreads();
 
     // ---- stream the item ------------------------------------------------------------------
+    // cut the buffer at this many entries (measured: k + k/4, k + k, k + 16 and k + 32 are all within
+    // 2 % of this up to top_k 100 and worse beyond; votes every third region gain 2 % from top_k 64 on)
+    const int trig = min(k + max(k >> 1, 16), CAP / 2);
     float thr = __uint_as_float(0xff800000u);            // -inf
     float rthr = thr;  // POST: the raw logit every column that can reach thr has at least
     const Post& POSTP = a.post;
 
-    if (nreg > 0) {
-        // The threshold the running histogram has reached (sampler_common.cuh).
-        auto fresh = [&]() {
-            const float t = *reinterpret_cast<const volatile float*>(&ctl->thr);
-            if (POST) {
-                if (t != thr) rthr = post_raw_bound(t, c.inv_temp, POSTP);
-            }
-            thr = t;
-        };
-        typedef VecPart<T> VP;
-        // One vector of a region in which this thread holds a column that reaches its threshold:
-        // one test on the vector's maximum, the compares only where it holds a survivor.
-        auto one_vector = [&](const uint4& v, float mu, int vec) {
-            if (POST ? (mu >= rthr) : (__fmul_rn(mu, c.inv_temp) >= thr))
-                filter_vec<S, T, POST>(v, vec, c.mis, c.inv_temp, thr, rthr);
-        };
-        // A complete region: one test per thread.  A rounded multiply by a positive factor is
-        // non-decreasing, so the largest scaled value is the scaled largest raw value, exactly.
-        auto whole_region = [&](const uint4(&src)[U], int r) {
-            typename VP::part_t part[U];
-#pragma unroll
-            for (int u = 0; u < U; u++) part[u] = VP::part(src[u]);
-            const float m = VP::template region<U>(part, src);
-            if (POST ? (m >= rthr) : (__fmul_rn(m, c.inv_temp) >= thr)) {
-                const int v0 = a0 + r * RV + tid;
-#pragma unroll
-                for (int u = 0; u < U; u++) one_vector(src[u], VP::finish(part[u], src[u]), v0 + u * NT);
-            }
-
-        };
-        // The item's last region: vectors beyond the end are skipped.
-        auto last_region = [&](const uint4(&src)[U], int r) {
+    if (!careful && nreg > 0) {
+        // later regions: the buffer already holds k entries >= thr with lower indices, so an equal
+        // value can no longer enter (sampler.go:268-275); one test per thread and region
+        auto later = [&](const uint4(&src)[U], int r) {
             const int v0 = a0 + r * RV + tid;
+            float mu[U];
+            float m = __uint_as_float(0xff800000u);
+            const bool whole = r + 1 < nreg;
 #pragma unroll
-            for (int u = 0; u < U; u++)
-                if (v0 + u * NT < b0) one_vector(src[u], vec_max_raw<T>(src[u]), v0 + u * NT);
+            for (int u = 0; u < U; u++) {
+                mu[u] = __uint_as_float(0x7fc00000u);  // NaN: beyond the item, admitted by no compare
+                if (whole || v0 + u * NT < b0) mu[u] = vec_max_raw<T>(src[u]);
+                m = fmaxf(m, mu[u]);
+            }
+            if (POST) {
+                if (m >= rthr) {
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+                        if (mu[u] >= rthr) cut::filter_vec_post<S, T, false>(src[u], v0 + u * NT, c, POSTP, rthr, thr, buf, ctl);
+                }
+            } else if (__fmul_rn(m, c.inv_temp) > thr) {
+                // A rounded multiply by a positive factor is non-decreasing, so the largest scaled value
+                // is the scaled largest raw value, exactly: one multiply per thread and region here,
+                // one per vector below, and the sixteen only where a vector holds a survivor.
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (__fmul_rn(mu[u], c.inv_temp) > thr) cut::filter_vec<S, T, false>(src[u], v0 + u * NT, c, thr, buf, ctl);
+            }
         };
-        // After region r one warp (they take turns) walks the histogram, if enough entries have come
-        // since the last walk, and raises the threshold; nobody waits for it.  The CTA meets only after
-        // regions 1, 2, 4, 8, ...: between two such meetings about k entries arrive however long the
-        // row is, and a meeting that finds the buffer more than half full compacts it.
-        auto region_end = [&](int r) {
-            // staged survivors are worked off once there are a few of them, after every one of the
-            // first regions (where the threshold moves fastest) and before the CTA meets
-            // (the count is taken by one lane after the warp has come together again: lanes that read it
-            // while others were still setting survivors aside would disagree on the call below, and a
-            // warp split over two of its own meeting points does not return)
-            __syncwarp();
-            const int staged = __shfl_sync(0xffffffffu, wcnt[warp], 0);
-            if (staged >= 16 || r < 8 || (r & (r - 1)) == 0) flush_staged<S, POST>();
-            if ((r & (NWARP - 1)) == warp) {
-                const int n = live_count(ctl);
-                const int fresh_entries = __shfl_sync(0xffffffffu, n - ctl->walked, 0);
-                const int kk = ctl->k;
-                if (fresh_entries >= (kk >> 4) + 2) {
-                    const uint32_t key = hist_threshold<S>(kk);
-                    if (lane == 0) {
-                        ctl->walked = n;
-                        if (key > ctl->thr_key) {
-                            atomicMax(&ctl->thr_key, key);
-                            ctl->thr = key2f(key);
-                        }
+        // one barrier per region; the thread that made the region's last append reads the final
+        // count before it arrives, so the OR is the same for every thread
+        auto region_end = [&](int lim) {
+            if (__syncthreads_or(live_count(ctl) >= lim)) {
+                if (live_count(ctl) > CAP) {
+                    careful = true;  // entries were dropped: redo the item on the careful path
+                } else {
+                    bool have;
+                    uint32_t kth = refresh_topk<S>(buf, ctl, hist, k, tid, &have);
+                    if (have) {
+                        thr = key2f(kth);
+                        if (POST) rthr = post_raw_bound(thr, c.inv_temp, POSTP);
                     }
                 }
             }
-            if ((r & (r - 1)) == 0) {
-                if (__syncthreads_or(live_count(ctl) > S::FORCE)) careful = forced_cut<S>(tid);
-            }
-            fresh();
         };
 
         // -- region 0 seeds the threshold --
-        if (nreg > 1) load_checked(rb, 1);
-        if (nreg > 1 && nwhole > 1) q += RV;
+        if (nreg > 1) load(rb, 1);
         {
             const int v0 = a0 + tid;
-            // The seed comes from RAW logits: everything between a raw logit and its final value
+            // Thread maxima of the RAW logits: everything between a raw logit and its final value
             // (post-processing up to its slack, penalty, temperature) is non-decreasing, and a
             // column's value is at least what it would be with the penalty, so the image of a raw
             // logit that k columns reach is a value that k columns reach -- no bitmap lookups here.
-            float t0, h0;  // raw: what k columns of the region reach, and what about half as many reach
-            if constexpr (!SEED_HIST) {
-                // Up to 32 * NWARP entries: from a sort of each warp's thread maxima.  NWARP * j >= k
-                // columns reach the smallest of the warps' j-th largest; the largest of their
-                // (j / 2)-th largest spans the bins, so that a few outliers do not stretch them.
-                float tmax = __uint_as_float(0xff800000u);
-#pragma unroll
-                for (int u = 0; u < U; u++)
-                    if (v0 + u * NT < b0) tmax = fmaxf(tmax, vec_max_raw<T>(ra[u]));
-                float x = tmax;  // bitonic sort across the warp, descending
-#pragma unroll
-                for (int k2 = 2; k2 <= 32; k2 <<= 1) {
-#pragma unroll
-                    for (int j2 = k2 >> 1; j2 > 0; j2 >>= 1) {
-                        float y = __shfl_xor_sync(0xffffffffu, x, j2);
-                        bool desc = (lane & k2) == 0;
-                        bool lower = (lane & j2) == 0;
-                        x = (lower == desc) ? fmaxf(x, y) : fminf(x, y);
-                    }
-                }
-                const int j = (k + NWARP - 1) / NWARP;
-                const float wj = __shfl_sync(0xffffffffu, x, j - 1);
-                const float wh = __shfl_sync(0xffffffffu, x, (j - 1) >> 1);
-                if (lane == 0) {
-                    ctl->warpv[warp] = wj;
-                    ctl->warpk_min[warp] = __float_as_uint(wh);
-                }
-                __syncthreads();
-                t0 = ctl->warpv[0];
-                h0 = __uint_as_float(ctl->warpk_min[0]);
-#pragma unroll
-                for (int w = 1; w < NWARP; w++) {
-                    t0 = fminf(t0, ctl->warpv[w]);
-                    h0 = fmaxf(h0, __uint_as_float(ctl->warpk_min[w]));
-                }
-            } else {
-                // Longer shortlists: every raw value of region 0 is counted in the histogram, laid
-                // over the region's own range, and every warp walks it for itself.
-                float lo = __uint_as_float(0x7f800000u), top = __uint_as_float(0xff800000u);
-#pragma unroll
-                for (int u = 0; u < U; u++) {
-                    if (v0 + u * NT < b0) {
-                        float raw[VEC];
-                        Elem<T>::widen(ra[u], raw);
-#pragma unroll
-                        for (int i = 0; i < VEC; i++) {
-                            if (raw[i] > -3.0e38f) lo = fminf(lo, raw[i]);
-                            top = fmaxf(top, raw[i]);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
-                    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
-                }
-                if (lane == 0) {
-                    ctl->warpv[warp] = top;
-                    ctl->warpk_min[warp] = __float_as_uint(lo);
-                }
-                __syncthreads();
-                lo = __uint_as_float(ctl->warpk_min[0]);
-                top = ctl->warpv[0];
-#pragma unroll
-                for (int w = 1; w < NWARP; w++) {
-                    lo = fminf(lo, __uint_as_float(ctl->warpk_min[w]));
-                    top = fmaxf(top, ctl->warpv[w]);
-                }
-                const float sc = (top > lo && top - lo < 3.0e38f) ? (float)HBINS / (top - lo) : 0.0f;
-                if (tid == 0) {
-                    ctl->hbase = lo;
-                    ctl->hscale = sc;
-                    ctl->hwidth = sc > 0.0f ? (top - lo) / (float)HBINS : 0.0f;
-                }
-#pragma unroll
-                for (int u = 0; u < U; u++) {
-                    if (v0 + u * NT < b0) {
-                        float raw[VEC];
-                        Elem<T>::widen(ra[u], raw);
-#pragma unroll
-                        for (int i = 0; i < VEC; i++)
-                            if (raw[i] >= lo) atomicAdd(&hist[hist_bin(raw[i], lo, sc)], 1u);
-                    }
-                }
-                __syncthreads();
-                const uint32_t kk = hist_threshold<S>(k);
-                const uint32_t kh = hist_threshold<S>((k + 1) >> 1);
-                // (with fewer than k columns in the region there is no seed)
-                t0 = kk ? key2f(kk) : __uint_as_float(0xff800000u);
-                h0 = kh ? key2f(kh) : top;
-                __syncthreads();
-                for (int i = tid; i < HBINS; i += NT) hist[i] = 0u;
-            }
-            if (POST) {
-                t0 = post_seed_logit(t0, POSTP);
-                h0 = post_seed_logit(h0, POSTP);
-            }
-            if (c.pen_bitmap) t0 = penalise(t0, c.pen);
-            t0 = __fmul_rn(t0, c.inv_temp);
-            h0 = __fmul_rn(h0, c.inv_temp);
-            if (tid == 0) {
-                // The bins of the running histogram start at the seed and span twelve times the
-                // distance to the value half as many columns reach: the k-th value of the whole row
-                // lies a few such distances up, and whatever lies beyond the span shares the top bin.
-                const float span = __fmul_rn(SEED_HIST ? 12.0f : 8.0f, __fsub_rn(h0, t0));
-                const bool ok = span > 0.0f && span < 3.0e38f;
-                ctl->thr_key = f2key(t0);
-                ctl->thr = t0;
-                ctl->hbase = t0;
-                ctl->htop = __fadd_rn(t0, span);
-                ctl->hscale = ok ? __fdiv_rn((float)HBINS, span) : 0.0f;
-                ctl->hwidth = ok ? __fdiv_rn(span, (float)HBINS) : 0.0f;
-            }
-            __syncthreads();
-            thr = t0;
-            if (POST) rthr = post_raw_bound(thr, c.inv_temp, POSTP);
+            float tmax = __uint_as_float(0xff800000u);
 #pragma unroll
             for (int u = 0; u < U; u++)
-                if (v0 + u * NT < b0) filter_vec<S, T, POST>(ra[u], v0 + u * NT, c.mis, c.inv_temp, thr, rthr);
-            flush_staged<S, POST>();
-        }
-        // the first meeting: every append of region 0 is counted before the threshold is read; every
-        // warp walks the histogram for itself
-        __syncthreads();
-        if (live_count(ctl) > CAP) {
-            careful = true;
-        } else {
-            const uint32_t key = hist_threshold<S>(k);
-            if (key > f2key(thr)) thr = key2f(key);
-            if (POST) rthr = post_raw_bound(thr, c.inv_temp, POSTP);
-            if (tid == 0) {
-                ctl->walked = live_count(ctl);
-                ctl->thr_key = f2key(thr);
-                ctl->thr = thr;
+                if (v0 + u * NT < b0) tmax = fmaxf(tmax, vec_max_raw<T>(ra[u]));
+            float x = tmax;  // bitonic sort across the warp, descending
+#pragma unroll
+            for (int k2 = 2; k2 <= 32; k2 <<= 1) {
+#pragma unroll
+                for (int j2 = k2 >> 1; j2 > 0; j2 >>= 1) {
+                    float y = __shfl_xor_sync(0xffffffffu, x, j2);
+                    bool desc = (lane & k2) == 0;
+                    bool lower = (lane & j2) == 0;
+                    x = (lower == desc) ? fmaxf(x, y) : fminf(x, y);
+                }
+            }
+            const int j = (k + NWARP - 1) / NWARP;
+            float wj = __shfl_sync(0xffffffffu, x, j - 1);
+            if (lane == 0) ctl->warpv[warp] = wj;
+            __syncthreads();
+            float t0 = ctl->warpv[0];
+#pragma unroll
+            for (int w = 1; w < NWARP; w++) t0 = fminf(t0, ctl->warpv[w]);
+            if (POST) t0 = post_seed_logit(t0, POSTP);
+            if (c.pen_bitmap) t0 = penalise(t0, c.pen);
+            t0 = __fmul_rn(t0, c.inv_temp);
+            if (POST) {
+                thr = t0;
+                rthr = post_raw_bound(thr, c.inv_temp, POSTP);
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (v0 + u * NT < b0) cut::filter_vec_post<S, T, true>(ra[u], v0 + u * NT, c, POSTP, rthr, thr, buf, ctl);
+            } else {
+                thr = t0;
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (v0 + u * NT < b0) cut::filter_vec<S, T, true>(ra[u], v0 + u * NT, c, thr, buf, ctl);
             }
         }
+        region_end(k + 1);
 
         // -- regions 1.. : two register sets, each refilled while the other is filtered --
-        int r = 1;  // rb holds region r
-        while (r + 2 < nwhole && !careful) {  // regions r + 1 and r + 2 are complete
-            load_whole(ra);
-            if (pf_lane && r + 3 < nwhole) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(pf + (size_t)(r + 3) * RV));
-            whole_region(rb, r);
-            region_end(r);
-            ++r;
-            if (careful) break;
-            load_whole(rb);
-            if (pf_lane && r + 3 < nwhole) asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(pf + (size_t)(r + 3) * RV));
-            whole_region(ra, r);
-            region_end(r);
-            ++r;
-        }
-        // the last regions (at most three), the item's end among them
+        // The barrier carries only the vote (the register sets are private), so it need not follow
+        // every region: the threshold is refreshed at most every VOTE_EVERY regions, at the price of
+        // a few more survivors under a threshold that is that much staler.
+        // (Measured and not kept: no periodic barrier at all -- a warp that finds the buffer at `trig`
+        // entries goes to the barrier and the others follow when they find the same, warps of one CTA
+        // drifting apart in between.  2 to 5 % faster at top_k 40 to 64, 1 to 2.5 % slower at 20 and
+        // 100, slower on the split-row batches.  Such a scheme must take the decision with a warp-wide
+        // vote: lanes of one warp that read the count at different moments reached different barrier
+        // instructions, which hung the kernel until the process was killed.)
+        int r = 1;
         while (r < nreg && !careful) {
-            if (r + 1 < nreg) load_checked(ra, r + 1);
+            if (r + 1 < nreg) load(ra, r + 1);
             ahead(r + 3);
-            if (r < nwhole) whole_region(rb, r);
-            else last_region(rb, r);
-            region_end(r);
+            later(rb, r);
+            if (r % VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
+            if (++r >= nreg || careful) break;
+            if (r + 1 < nreg) load(rb, r + 1);
+            ahead(r + 3);
+            later(ra, r);
+            if (r % VOTE_EVERY == 0 || r + 1 == nreg) region_end(trig);
             ++r;
-#pragma unroll
-            for (int u = 0; u < U; u++) rb[u] = ra[u];
         }
     }
 
     if (!careful) {
-        flush_staged<S, POST>();
         // the columns of the partial vectors at the ends of this item
         int r1_lo = elo, r1_hi = ehi, r2_lo = ehi, r2_hi = ehi;
         if (b0 > a0) {
@@ -386,12 +344,16 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
         if (tid < n1 + n2) {  // at most 4 * VEC columns
             int e = tid < n1 ? r1_lo + tid : r2_lo + (tid - n1);
             float raw = Elem<T>::load1(c.row, e);
-            if (POST ? (raw >= rthr) : (__fmul_rn(raw, c.inv_temp) >= thr)) survivor<S, POST>(raw, e);
+            if (POST) {
+                if (raw >= rthr) cut::consider_post<S, true>(buf, ctl, c, POSTP, raw, e, thr);
+            } else {
+                float v = __fmul_rn(raw, c.inv_temp);
+                if (v >= thr) cut::consider<S, true>(buf, ctl, c, raw, v, e, thr);
+            }
         }
         __syncthreads();
-        // what the histogram's threshold leaves is a few entries more than k: the exact cut's work
-        if (live_count(ctl) > k + 32) careful = hist_compact<S>(buf, ctl, hist, tid, false);
-        else __syncthreads();
+        if (live_count(ctl) > CAP) careful = true;
+        __syncthreads();
     }
 
     if (careful) {  // the careful path: steps that always fit the buffer
