@@ -240,9 +240,17 @@ int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
 }
 
 // The streaming kernel, and its shape, that serve the batch's longest shortlist.
+// Items of a few regions (split rows, narrow vocabulary shards) take the kernel with exact cuts at
+// any shortlist length its shape serves: the other kernel's histogram pays off over a long item.
+bool cut_kernel(const KArgs& a, int dtype) {
+    if (a.max_top_k <= CUT_KMAX) return true;
+    const int per_region = ShapeK256::NT * ShapeK256::U * (dtype == MANTLE_DTYPE_F32 ? 4 : 8);
+    return a.max_top_k <= ShapeK256::KCAP && a.vocab / a.splits <= 8 * per_region;
+}
+
 template <int MODE>
 int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
-    if (a.max_top_k <= CUT_KMAX) return launch_scan_shape<ShapeK256, MODE, true>(a, dtype, stream);
+    if (cut_kernel(a, dtype)) return launch_scan_shape<ShapeK256, MODE, true>(a, dtype, stream);
     if (small_shape(a.max_top_k)) return launch_scan_shape<ShapeK256, MODE, false>(a, dtype, stream);
     return launch_scan_shape<ShapeK1024, MODE, false>(a, dtype, stream);
 }
@@ -338,7 +346,10 @@ extern "C" int mantleCudaSamplerSplits(const MantleSampleBatch* batch, int* spli
 extern "C" const char* mantleCudaSamplerKernelName(const MantleSampleBatch* batch) {
     if (!batch_ok(batch, true)) return "";
     if (batch->max_top_k > KMAX) return "wide_hist_kernel";
-    return batch->max_top_k <= CUT_KMAX ? "scan_rows_ldg_kernel" : "scan_rows_hist_kernel";
+    KArgs a;
+    fill_args(a, batch);
+    a.splits = choose_splits(batch);
+    return cut_kernel(a, batch->dtype) ? "scan_rows_ldg_kernel" : "scan_rows_hist_kernel";
 }
 
 extern "C" int mantleCudaSamplerWorkspaceBytes(const MantleSampleBatch* batch, size_t* bytes) {

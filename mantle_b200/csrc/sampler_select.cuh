@@ -235,17 +235,18 @@ __device__ __forceinline__ uint32_t rank_select2(Cand* buf, Ctl* ctl, int n, int
 
 // Cut the buffer to its k best entries, by counting when it is small and by radix select
 // otherwise.  Called by every thread with the buffer quiescent.
-template <class S>
+// RANK2: buffers of up to twice as many entries are still ranked by counting, two entries per thread.
+template <class S, bool RANK2 = false>
 __device__ __forceinline__ uint32_t refresh_topk(Cand* buf, Ctl* ctl, uint32_t* hist, int k, int tid,
                                                  bool* have_kth, bool* ordered = nullptr) {
     __syncthreads();
     const int n = live_count(ctl);
     __syncthreads();
-    constexpr int RANK2 = S::NT == RANK_MAX ? 2 * RANK_MAX : RANK_MAX;
-    if (ordered) *ordered = n <= RANK2;  // the counting select leaves its survivors in order
+    constexpr int RANKED = (RANK2 && S::NT == RANK_MAX) ? 2 * RANK_MAX : RANK_MAX;
+    if (ordered) *ordered = n <= RANKED;  // the counting select leaves its survivors in order
     if (n <= RANK_MAX) return rank_select(buf, ctl, n, k, tid, have_kth);
-    if constexpr (S::NT == RANK_MAX) {
-        if (n <= RANK2) return rank_select2<S>(buf, ctl, n, k, tid, have_kth);
+    if constexpr (RANKED > RANK_MAX) {
+        if (n <= RANKED) return rank_select2<S>(buf, ctl, n, k, tid, have_kth);
     }
     return select_topk<S>(buf, ctl, hist, k, tid, have_kth);
 }
@@ -324,7 +325,7 @@ __device__ __noinline__ bool forced_cut(int tid) {
     if (live_count(ctl) <= S::FORCE) return false;
     bool have;
     if (tid == 0) ctl->kmax = 0u;
-    const uint32_t kth = refresh_topk<S>(buf, ctl, hist, ctl->k, tid, &have);
+    const uint32_t kth = refresh_topk<S, true>(buf, ctl, hist, ctl->k, tid, &have);
     const int left = live_count(ctl);
     uint32_t top_key = 0u;
     for (int i = tid; i < left; i += S::NT) top_key = max(top_key, buf[i].key);

@@ -428,7 +428,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
     }
 
     bool have, ordered;
-    refresh_topk<S>(buf, ctl, hist, k, tid, &have, &ordered);
+    refresh_topk<S, true>(buf, ctl, hist, k, tid, &have, &ordered);
     __syncthreads();
     if (bad_k) {
         if (tid == 0) {
