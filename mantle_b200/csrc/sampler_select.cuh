@@ -333,8 +333,11 @@ __device__ __noinline__ bool forced_cut(int tid) {
     __syncthreads();
     if (tid == 0 && have) {
         // the bins now span what the cut left: its k-th value to its largest
-        ctl->thr_key = max(ctl->thr_key, kth + 1u);
-        ctl->thr = key2f(ctl->thr_key);
+        // thr_key is also what a later compaction keeps entries by: it stays at the k-th key, which
+        // the cut's own ties carry; only the admission threshold moves past it
+        const uint32_t keep = max(ctl->thr_key, kth);
+        ctl->thr_key = keep;
+        ctl->thr = key2f(max(keep, kth + 1u));
         const float base = key2f(kth), top = key2f(ctl->kmax);
         const bool ok = top > base && top - base < 3.0e38f;
         ctl->hbase = base;

@@ -186,6 +186,70 @@ def test_adversarial_rows(kind):
                              cand_cap=1024 if kind == "huge_k" else 200, splits=splits, where=kind)
 
 
+@pytest.mark.parametrize("max_k", [64, 224, 1024])
+@pytest.mark.parametrize("kind", ["step_up", "outlier", "plateau", "slow_ramp", "few_levels", "masked"])
+def test_histogram_kernel_hazards(kind, max_k):
+    """Rows built against the kernel whose threshold comes from a running histogram of the candidate
+    buffer (shortlists above 32 entries): a first region far below the rest of the row, an outlier
+    that stretches the bins, the k-th value repeated thousands of times, a slow upward trend that
+    keeps the buffer filling, a handful of distinct values, most of the row masked to -inf."""
+    rng = np.random.default_rng(4242 + max_k)
+    rows, V = 5, 70001
+    base = (rng.standard_normal((rows, V)) * 2).astype(np.float32)
+    if kind == "step_up":
+        logits = base.copy()
+        logits[:, :13000] -= 40.0
+    elif kind == "outlier":
+        logits = base.copy()
+        logits[:, 17] = 3.0e30
+        logits[:, 50000] = 1.0e6
+    elif kind == "plateau":
+        logits = base.copy()
+        for r in range(rows):
+            v = np.sort(logits[r])[-(max_k // 2 + 3)]  # a value inside every shortlist
+            logits[r, rng.choice(V, size=6000, replace=False)] = v
+    elif kind == "slow_ramp":
+        logits = base * 0.05 + np.linspace(-8, 8, V, dtype=np.float32)[None, :]
+    elif kind == "few_levels":
+        logits = rng.choice(np.array([-1.0, 0.0, 0.5, 0.75, 3.0], dtype=np.float32), size=(rows, V),
+                            p=[0.3, 0.3, 0.2, 0.19, 0.01])
+    else:
+        logits = np.full((rows, V), -np.inf, dtype=np.float32)
+        keep = rng.choice(V, size=max_k + 40, replace=False)
+        logits[:, keep] = base[:, keep]
+    ks = (33, max_k // 2, max_k)
+    params = random_params(rng, rows, ks=ks)
+    hist = rng.integers(0, V, size=(rows, 200)).astype(np.int32)
+    for splits in (1, 2):
+        check_against_oracle(logits.astype(np.float32), params, max_k, history=hist, cand_cap=max_k, splits=splits,
+                             where="%s max_k %d splits %d" % (kind, max_k, splits))
+
+
+@pytest.mark.parametrize("seed", range(4))
+@pytest.mark.parametrize("max_k", [224, 1024])
+def test_histogram_kernel_random_rows(seed, max_k):
+    """Random rows of random texture (value granularity from float32 noise down to a few levels, a
+    random share masked to -inf, a random trend along the row) at every shortlist length the
+    histogram kernel serves, in both of its shapes."""
+    rng = np.random.default_rng(9000 + 10 * seed + max_k)
+    rows = 20
+    V = int(rng.choice([50000, 151936, 262144]))
+    logits = (rng.standard_normal((rows, V)) * 3).astype(np.float32)
+    for r in range(rows):
+        step = float(rng.choice([0.0, 0.0, 1.0 / 64, 0.25, 1.0]))
+        if step:
+            logits[r] = np.round(logits[r] / step) * step
+        logits[r] += np.linspace(0, float(rng.choice([0.0, 0.0, 6.0, -6.0])), V, dtype=np.float32)
+        share = float(rng.choice([0.0, 0.0, 0.3, 0.9]))
+        if share:
+            logits[r, rng.random(V) < share] = -np.inf
+    ks = (33, 40, 64, 100, 200, 224) if max_k == 224 else (225, 256, 400, 512, 1000, 1024)
+    params = random_params(rng, rows, ks=ks)
+    hist = rng.integers(0, V, size=(rows, 300)).astype(np.int32)
+    check_against_oracle(logits, params, max_k, history=hist, cand_cap=max_k,
+                         where="seed %d V %d max_k %d" % (seed, V, max_k))
+
+
 # ---- the benchmark configurations ---------------------------------------------------------------------
 
 def test_config_single_row():
