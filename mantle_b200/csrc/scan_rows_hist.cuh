@@ -1,4 +1,5 @@
-// scan_rows_hist_kernel: the streaming pass with plain 16-byte loads; the default kernel.
+// scan_rows_hist_kernel: the streaming pass for shortlists of 33 to 1024 entries, with plain 16-byte
+// loads and a threshold that comes from a running histogram of the candidate buffer.
 // Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
 // translation unit.
 #pragma once
@@ -6,10 +7,19 @@
 namespace {
 
 // ---------------------------------------------------------------------------------------
-// The streaming pass: one CTA per item (row, split), plain 16-byte loads, two register sets per
-// thread, each refilled from global memory while the other is filtered, a barrier every second
-// region of NT*U vectors.  No shared-memory staging, so the CTA is small (candidate buffer +
-// bitmap) and four of them share an SM.
+// One CTA per item (row, split), plain 16-byte loads, two register sets per thread, each refilled
+// from global memory while the other is filtered.  No shared-memory staging of the row, so the
+// CTA is small (candidate buffer, histogram, staged survivors, bitmap) and four of them share an SM.
+//
+// Where scan_rows_ldg_kernel cuts its buffer exactly whenever it fills -- which ranks n entries
+// against each other, n growing with the shortlist -- this kernel never ranks anything while the
+// row streams.  Every entry that enters the buffer is counted in a histogram of its value; one
+// warp per region walks the counts from the top to the bin at which they reach k and raises the
+// threshold to that bin's edge (sampler_common.cuh: hist_bin, hist_threshold); the buffer keeps
+// every entry ever admitted and is compacted by the last threshold once, before the one exact
+// select at the end of the row.  A lane that finds a survivor only sets it aside; its warp works
+// the staged survivors off together between two regions (stage, flush_staged).  The CTA meets at
+// a barrier only after regions 1, 2, 4, 8, ... (sampler_select.cuh: forced_cut).
 
 template <class S, typename T, int MODE, bool POST>
 __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KArgs a) {
