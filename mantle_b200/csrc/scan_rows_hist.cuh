@@ -158,6 +158,14 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
         // A complete region: one test per thread.  A rounded multiply by a positive factor is
         // non-decreasing, so the largest scaled value is the scaled largest raw value, exactly.
         auto whole_region = [&](const uint4(&src)[U], int r) {
+            if constexpr (SEED_HIST) {
+                // The larger shape's shortlists are long enough that nearly every warp holds a survivor in
+                // nearly every vector: the tests in front of the compares only cost there.
+                const int v0 = a0 + r * RV + tid;
+#pragma unroll
+                for (int u = 0; u < U; u++) filter_vec<S, T, POST>(src[u], v0 + u * NT, c.mis, c.inv_temp, thr, rthr);
+                return;
+            }
             typename VP::part_t part[U];
 #pragma unroll
             for (int u = 0; u < U; u++) part[u] = VP::part(src[u]);
