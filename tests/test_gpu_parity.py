@@ -302,6 +302,39 @@ def test_full_size_properties():
     assert np.all(a["cand_idx"][np.arange(rows), pos] == a["next"]) and np.all(pos < a["cut"])
 
 
+@pytest.mark.parametrize("top_k", [100, 600])
+def test_full_size_properties_long_shortlists(top_k):
+    """The same 4096 x 151936 batch with longer shortlists (the kernel with the running histogram,
+    in both of its shapes): idempotence, a strided sample against the oracle, row permutation, and
+    every row's shortlist ids equal to torch's top-k ids as a set wherever the k-th value is unique."""
+    w = workloads.make("throughput", device=DEV)
+    rows = w.rows
+    params = w.params.copy()
+    params["top_k"] = top_k
+    hist = w.history.cpu().numpy()
+    a = run_gpu(w.logits, params, top_k, history=hist, cand_cap=top_k)
+    b = run_gpu(w.logits, params, top_k, history=hist, cand_cap=top_k)
+    for key in ("next", "n_kept", "cut", "cand_idx", "cand_prob"):
+        assert np.array_equal(a[key], b[key])
+    assert a["status"] == 0 and np.all(a["n_kept"] == top_k) and np.all(a["cut"] >= 1)
+    sel = np.arange(0, rows, 97)
+    ref = O.sample_rows(w.logits[sel].cpu().numpy(), params[sel], history=hist[sel], cand_cap=top_k)
+    sub = {k: (v[sel] if isinstance(v, np.ndarray) else v) for k, v in a.items()}
+    compare(sub, ref, top_k)
+    perm = torch.randperm(rows, generator=torch.Generator().manual_seed(5))
+    c = run_gpu(w.logits[perm.to(DEV)].contiguous(), params[perm.numpy()], top_k, history=hist[perm.numpy()], cand_cap=0)
+    assert np.array_equal(c["next"], a["next"][perm.numpy()])
+    # shortlist ids against torch on rows without a penalty window (the first 64 have their history cleared)
+    p2 = params[:64].copy()
+    p2["repeat_penalty"] = 1.0
+    d = run_gpu(w.logits[:64].contiguous(), p2, top_k, cand_cap=top_k)
+    vals, ids = torch.topk(w.logits[:64], top_k + 1, dim=1)
+    unique_kth = (vals[:, top_k - 1] > vals[:, top_k]).cpu().numpy()
+    got = np.sort(d["cand_idx"][:, :top_k], axis=1)
+    want = np.sort(ids[:, :top_k].cpu().numpy(), axis=1)
+    assert unique_kth.any() and np.array_equal(got[unique_kth], want[unique_kth])
+
+
 # ---- stand-alone entry points ---------------------------------------------------------------------------
 
 def test_argmax_rows():
