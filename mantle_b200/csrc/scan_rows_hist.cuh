@@ -189,14 +189,13 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
         // regions 1, 2, 4, 8, ...: between two such meetings about k entries arrive however long the
         // row is, and a meeting that finds the buffer more than half full compacts it.
         auto region_end = [&](int r) {
-            // staged survivors are worked off once there are a few of them, after every one of the
-            // first regions (where the threshold moves fastest) and before the CTA meets
+            // staged survivors are worked off once the area is three quarters full, and before the CTA meets
             // (the count is taken by one lane after the warp has come together again: lanes that read it
             // while others were still setting survivors aside would disagree on the call below, and a
             // warp split over two of its own meeting points does not return)
             __syncwarp();
             const int staged = __shfl_sync(0xffffffffu, wcnt[warp], 0);
-            if (staged >= 16 || r < 8 || (r & (r - 1)) == 0) flush_staged<S, POST>();
+            if (staged >= 24 || (r & (r - 1)) == 0) flush_staged<S, POST>();
             if ((r & (NWARP - 1)) == warp) {
                 const int n = live_count(ctl);
                 const int fresh_entries = __shfl_sync(0xffffffffu, n - ctl->walked, 0);
