@@ -1,4 +1,4 @@
-// scan_rows_hist_kernel: the streaming pass for shortlists of 33 to 1024 entries, with plain 16-byte
+// scan_rows_hist_kernel: the streaming pass for shortlists of 29 to 1024 entries, with plain 16-byte
 // loads and a threshold that comes from a running histogram of the candidate buffer.
 // Part of the device-side logits sampler; included by sampler_kernels.cu, in this order, into one
 // translation unit.

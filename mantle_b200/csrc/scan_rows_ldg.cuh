@@ -10,9 +10,9 @@ namespace {
 // many entries again: the cuts rank a few dozen entries and give the exact k-th value as the next
 // threshold.  Longer shortlists go to scan_rows_hist_kernel, whose threshold comes from a running
 // histogram and which never ranks more than the final shortlist (measured on 4096 rows of 151 936
-// float32 columns: 0.405 against 0.428 ms at top_k 20, 0.470 against 0.454 ms at 40, 0.721
-// against 0.531 ms at 100).
-constexpr int CUT_KMAX = 32;
+// float32 columns: 0.405 against 0.420 ms at top_k 20, 0.428 against 0.430 ms at 28, 0.439 against
+// 0.435 ms at 32, 0.470 against 0.446 ms at 40, 0.721 against 0.522 ms at 100).
+constexpr int CUT_KMAX = 28;
 constexpr int VOTE_EVERY = 2;  // regions between two "does the buffer need a cut" votes
 
 namespace cut {

@@ -190,7 +190,7 @@ def test_adversarial_rows(kind):
 @pytest.mark.parametrize("kind", ["step_up", "outlier", "plateau", "slow_ramp", "few_levels", "masked"])
 def test_histogram_kernel_hazards(kind, max_k):
     """Rows built against the kernel whose threshold comes from a running histogram of the candidate
-    buffer (shortlists above 32 entries): a first region far below the rest of the row, an outlier
+    buffer (shortlists above 28 entries): a first region far below the rest of the row, an outlier
     that stretches the bins, the k-th value repeated thousands of times, a slow upward trend that
     keeps the buffer filling, a handful of distinct values, most of the row masked to -inf."""
     rng = np.random.default_rng(4242 + max_k)
