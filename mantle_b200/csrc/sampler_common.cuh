@@ -32,7 +32,8 @@ struct Shape {
     static constexpr size_t WCNT_OFF = STG_OFF + 8 * (size_t)(NWARP * STG);
     static constexpr size_t SMEM_FIXED = WCNT_OFF + ((4 * (size_t)NWARP + 15) & ~(size_t)15);
     // the streaming loop compacts the buffer at its next meeting once it holds this many entries
-    static constexpr int FORCE = CAP / 2;
+    // (the shape for shortlists of up to 224 entries sees at most that many arrive between two meetings)
+    static constexpr int FORCE = KCAP > 256 ? CAP / 2 : CAP / 4 * 3;
 };
 // Four small CTAs per SM overlap the serial phases of a row (bitmap, cuts, tail) with the
 // streaming of three other rows; measured against three CTAs fed by a ring of bulk copies

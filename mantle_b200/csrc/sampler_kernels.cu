@@ -223,7 +223,9 @@ int launch_scan_as(const KArgs& a, cudaStream_t stream) {
     const size_t smem = S::SMEM_FIXED + bitmap_words(a.vocab) * sizeof(uint32_t);
     const long long items = (long long)a.rows * a.splits;
     if (items > 0x7fffffffLL) return kInvalid;
-    auto kern = CUT ? scan_rows_ldg_kernel<S, T, MODE, POST> : scan_rows_hist_kernel<S, T, MODE, POST>;
+    void (*kern)(const KArgs);
+    if constexpr (CUT) kern = scan_rows_ldg_kernel<S, T, MODE, POST>;
+    else kern = scan_rows_hist_kernel<S, T, MODE, POST>;
     const int rc = ensure_smem(kern, smem, granted);
     if (rc) return rc;
     kern<<<(int)items, S::NT, smem, stream>>>(a);

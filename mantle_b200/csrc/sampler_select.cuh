@@ -6,6 +6,14 @@
 
 namespace {
 
+// a precedes b in the shortlist order (key descending, index ascending).  By value and without
+// short-circuits: an entry read through a reference to shared memory became two dependent loads
+// and a branch per compare, which cost the split-row batches a seventh of their time.
+__device__ __forceinline__ bool cand_before(const Cand a, const Cand b) {
+    return (a.key > b.key) | ((a.key == b.key) & (a.idx < b.idx));
+}
+
+
 // ---------------------------------------------------------------------------------------
 // Shared-memory radix select: cut the candidate buffer to its k best entries in the order
 // (key descending, index ascending).  Called by every thread of the CTA with the buffer
@@ -309,6 +317,121 @@ __device__ __forceinline__ bool hist_compact(Cand* buf, Ctl* ctl, uint32_t* hist
     return false;
 }
 
+// Orders the n entries of the buffer (key descending, index ascending) and keeps the best k, for a
+// buffer too long for the counting select: the entries are dealt into HBINS buckets of their value
+// (laid over the buffer's own range), bucket by bucket into the upper half of the buffer, and every
+// thread then orders one bucket by insertion.  n * (a bucket's length) compares in all, four
+// barriers; the radix select followed by the bitonic sort it replaces has sixty.  Returns false, with
+// the buffer as it was, when that does not work out (more than half the buffer in use, a bucket of
+// more than BUCKET_MAX entries: ties, or one value far from the rest); the caller then takes the
+// other way.  Every thread; the buffer quiescent.
+constexpr int BUCKET_MAX = 48;
+template <class S>
+__device__ __noinline__ bool bucket_order(int k, int tid) {
+    static_assert(S::NT == HBINS, "one bucket per thread");
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Cand* buf = reinterpret_cast<Cand*>(smem_raw);
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(buf + S::CAP);                 // the histogram's words
+    uint32_t* off = reinterpret_cast<uint32_t*>(smem_raw + S::STG_OFF);      // the staging area: free by now
+    static_assert(8 * S::NWARP * S::STG >= 4 * HBINS, "the offsets fit the staging area");
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + S::CTL_OFF);
+    Cand* dst = buf + S::CAP / 2;
+    constexpr int NT = S::NT, EPT = (S::CAP / 2 + NT - 1) / NT;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int n = live_count(ctl);
+    if (n > S::CAP / 2) return false;
+
+    // the range of the keys
+    uint32_t lo = 0xffffffffu, hi = 0u;
+    for (int i = tid; i < n; i += NT) {
+        const uint32_t key = buf[i].key;
+        lo = min(lo, key);
+        hi = max(hi, key);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    if (lane == 0) {
+        ctl->warpk_min[warp] = lo;
+        ctl->warpk_max[warp] = hi;
+    }
+    cnt[tid] = 0u;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < S::NWARP; w++) {
+        lo = min(lo, ctl->warpk_min[w]);
+        hi = max(hi, ctl->warpk_max[w]);
+    }
+    const float flo = key2f(lo), fhi = key2f(hi);
+    const float span = __fsub_rn(fhi, flo);
+    const float sc = (span > 0.0f && span < 3.0e38f) ? __fmul_rn(__fdiv_rn((float)HBINS, span), 1.0f - 1e-6f) : 0.0f;
+
+    // every entry takes a place in its bucket
+    uint32_t place[EPT];  // bucket << 16 | place in it
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        const int i = tid + j * NT;
+        if (i < n) {
+            const int b = hist_bin(key2f(buf[i].key), flo, sc);
+            place[j] = ((uint32_t)b << 16) | atomicAdd(&cnt[b], 1u);
+        }
+    }
+    __syncthreads();
+    // where a bucket starts: behind all higher ones
+    if (warp == 0) {
+        uint32_t c[8], tot = 0, most = 0;
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            c[b] = cnt[lane * 8 + b];
+            tot += c[b];
+            most = max(most, c[b]);
+        }
+        uint32_t above = tot;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t y = __shfl_down_sync(0xffffffffu, above, o);
+            if (lane + o < 32) above += y;
+            most = max(most, __shfl_xor_sync(0xffffffffu, most, o));
+        }
+        uint32_t run = above - tot;
+#pragma unroll
+        for (int b = 7; b >= 0; b--) {
+            off[lane * 8 + b] = run;
+            run += c[b];
+        }
+        if (lane == 0) ctl->sel_cnt = (int)most;
+    }
+    __syncthreads();
+    if (ctl->sel_cnt > BUCKET_MAX) return false;
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        const int i = tid + j * NT;
+        if (i < n) dst[off[place[j] >> 16] + (place[j] & 0xffffu)] = buf[i];
+    }
+    __syncthreads();
+    {   // one bucket per thread, by insertion
+        const int m = (int)cnt[tid];
+        Cand* seg = dst + off[tid];
+        for (int a = 1; a < m; a++) {
+            const Cand x = seg[a];
+            int c = a - 1;
+            while (c >= 0 && cand_before(x, seg[c])) {
+                seg[c + 1] = seg[c];
+                c--;
+            }
+            seg[c + 1] = x;
+        }
+    }
+    __syncthreads();
+    const int m = min(n, k);
+    for (int i = tid; i < m; i += NT) buf[i] = dst[i];
+    if (tid == 0) ctl->cnt = m;
+    __syncthreads();
+    return true;
+}
+
 // A meeting of the streaming loop at which the buffer holds more than FORCE entries: compact it by
 // the histogram's threshold and, if that does not free it (values tied in their thousands, bins
 // too coarse for this row), cut it exactly and lay the bins over what is left.  Every warp is
@@ -348,13 +471,6 @@ __device__ __noinline__ bool forced_cut(int tid) {
     __syncthreads();
     hist_rebuild<S>(buf, ctl, hist, live_count(ctl), tid);
     return false;
-}
-
-// a precedes b in the shortlist order (key descending, index ascending).  By value and without
-// short-circuits: an entry read through a reference to shared memory became two dependent loads
-// and a branch per compare, which cost the split-row batches a seventh of their time.
-__device__ __forceinline__ bool cand_before(const Cand a, const Cand b) {
-    return (a.key > b.key) | ((a.key == b.key) & (a.idx < b.idx));
 }
 
 // Bitonic sort of the first n entries of the buffer into the shortlist order, in place; the

@@ -444,8 +444,13 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
         __syncthreads();
     }
 
-    bool have, ordered;
-    refresh_topk<S, true>(buf, ctl, hist, k, tid, &have, &ordered);
+    bool have, ordered = false;
+    if constexpr (SEED_HIST) {
+        // long shortlists: the buckets order what the counting select cannot take
+        __syncthreads();
+        if (!careful && live_count(ctl) > 2 * RANK_MAX) ordered = bucket_order<S>(k, tid);
+    }
+    if (!ordered) refresh_topk<S, true>(buf, ctl, hist, k, tid, &have, &ordered);
     __syncthreads();
     if (bad_k) {
         if (tid == 0) {
