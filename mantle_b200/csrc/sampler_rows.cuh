@@ -104,20 +104,25 @@ __device__ void build_penalty_bitmap(const KArgs& a, int row, const WinPlan& w, 
     __syncthreads();
 }
 
-// The same bitmap for the plain-load kernel, arranged for latency: the window's ids are requested
-// first and travel while the bitmap is zeroed (with 16-byte stores); the barrier after the clears
-// is the caller's.  (Measured: the bitmap phase cost a tenth of the kernel's time before.)
+// The same bitmap for the streaming kernels, arranged for latency.  The most recent HIST_PRE * NT ids of
+// the row's history are requested at the very start of the kernel (history_tail), before the row's
+// parameters -- which say how long the window is -- have arrived, so that the two loads travel together
+// instead of one behind the other (measured under load: several thousand cycles each); they also travel
+// while the bitmap is zeroed (with 16-byte stores).  The barrier after the clears is the caller's.
+constexpr int HIST_PRE = 4;
+template <int NT>
+__device__ __forceinline__ void history_tail(const KArgs& a, int row, int hl, int tid, int (&ids)[HIST_PRE]) {
+    const int32_t* h = a.history + (size_t)row * (size_t)a.hist_stride;
+#pragma unroll
+    for (int u = 0; u < HIST_PRE; u++) {
+        const int j = hl - 1 - (u * NT + tid);
+        ids[u] = j >= 0 ? __ldg(h + j) : -1;
+    }
+}
 template <int NT>
 __device__ __forceinline__ void build_penalty_bitmap_early(const KArgs& a, int row, const WinPlan& w, int hl, int V,
-                                                           int voff, uint32_t* bm, int tid) {
-    constexpr int PRE = 4;  // ids per thread fetched ahead: windows of up to PRE * NT ids
+                                                           int voff, uint32_t* bm, int tid, const int (&ids)[HIST_PRE]) {
     const int32_t* h = a.history + (size_t)row * (size_t)a.hist_stride;
-    int ids[PRE];
-#pragma unroll
-    for (int u = 0; u < PRE; u++) {
-        const int j = w.start + u * NT + tid;
-        ids[u] = j < hl ? __ldg(h + j) : -1;
-    }
     uint4* bm4 = reinterpret_cast<uint4*>(bm);
     const int nvec = (int)(bitmap_words(V) / 4);
     for (int i = tid; i < nvec; i += NT) bm4[i] = make_uint4(0, 0, 0, 0);
@@ -129,8 +134,9 @@ __device__ __forceinline__ void build_penalty_bitmap_early(const KArgs& a, int r
         }
     };
 #pragma unroll
-    for (int u = 0; u < PRE; u++) mark(ids[u]);
-    for (int j = w.start + PRE * NT + tid; j < hl; j += NT) mark(h[j]);
+    for (int u = 0; u < HIST_PRE; u++)
+        if (hl - 1 - (u * NT + tid) >= w.start) mark(ids[u]);  // inside the window (sampler.go:100-101)
+    for (int j = w.start + tid; j < hl - HIST_PRE * NT; j += NT) mark(h[j]);  // what a longer window holds beyond
     if (a.n_exclude > 0) {  // sampler.go:122-126, after every set
         __syncthreads();
         for (int j = tid; j < a.n_exclude; j += NT) {

@@ -47,6 +47,10 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
         }
         return;
     }
+    // the history's most recent ids are asked for before anything else is
+    const int hl = history_len(a, row);
+    int recent[HIST_PRE];
+    if (hl > 0) history_tail<NT>(a, row, hl, tid, recent);
     const MantleSampleParams P = row_params(a, row);
     bool greedy, bad_k;
     const int k = row_k(a, P, S::KCAP, &greedy, &bad_k);
@@ -117,10 +121,9 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
     if (tid < NWARP) wcnt[tid] = 0;
 
     // ---- repeat penalty: bitmap of the de-duplicated window (sampler.go:99-138) --------
-    const int hl = history_len(a, row);
     const WinPlan wp = win_plan(P, hl);
     if (wp.active) {
-        build_penalty_bitmap_early<NT>(a, row, wp, hl, c.V, c.voff, bm, tid);
+        build_penalty_bitmap_early<NT>(a, row, wp, hl, c.V, c.voff, bm, tid, recent);
         c.pen_bitmap = true;
     }
     if (tid == 0) {  // what the out-of-line survivor code reads
