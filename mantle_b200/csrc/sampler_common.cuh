@@ -26,7 +26,10 @@ struct Shape {
     static_assert(KCAP * 24 <= CAP * 8, "ordered shortlist must fit behind the survivors");
     static_assert(RANK_MAX <= NT, "counting select: one entry per thread");
     // shared memory: [Cand buf[CAP]] [hist[HBINS]] [Ctl] [staged survivors[NWARP][STG]] [their counts[NWARP]] [bitmap]
-    static constexpr int STG = 32;  // raw survivors a warp sets aside before it works them off together
+    // raw survivors a warp sets aside before it works them off together.  (Sixty-four in the smaller shape
+    // were measured slower at every shortlist length, the other kernel included: four CTAs of 41 KB push the
+    // SM's shared-memory carve-out from 164 to 196 KB and leave the L1 a third less.)
+    static constexpr int STG = 32;
     static constexpr size_t CTL_OFF = 8 * (size_t)CAP + 4 * (size_t)HBINS;
     static constexpr size_t STG_OFF = CTL_OFF + 512;
     static constexpr size_t WCNT_OFF = STG_OFF + 8 * (size_t)(NWARP * STG);
@@ -443,34 +446,36 @@ __device__ __noinline__ void flush_staged() {
     __syncwarp();
     const int n = min(*reinterpret_cast<volatile int*>(wc), S::STG);
     if (n == 0) return;
-    bool pass = false;
-    float v = 0.0f;
-    int e = 0;
-    if (lane < n) {
-        const uint2 st = reinterpret_cast<const uint2*>(smem_raw + S::STG_OFF)[warp * S::STG + lane];
-        e = (int)st.y;
-        float l = __uint_as_float(st.x);
-        if (POST) {
-            const Post post = {ctl->post_mode, ctl->post_scale, ctl->post_cap};
-            l = post_logit(l, post);
+    for (int first = 0; first < n; first += 32) {  // 32 staged survivors at a time, one per lane
+        bool pass = false;
+        float v = 0.0f;
+        int e = 0;
+        if (first + lane < n) {
+            const uint2 st = reinterpret_cast<const uint2*>(smem_raw + S::STG_OFF)[warp * S::STG + first + lane];
+            e = (int)st.y;
+            float l = __uint_as_float(st.x);
+            if (POST) {
+                const Post post = {ctl->post_mode, ctl->post_scale, ctl->post_cap};
+                l = post_logit(l, post);
+            }
+            if (ctl->pen_on && bm_test(bm, e)) l = penalise(l, ctl->pen);
+            v = __fmul_rn(l, ctl->inv_temp);
+            pass = v >= *reinterpret_cast<const volatile float*>(&ctl->thr);
         }
-        if (ctl->pen_on && bm_test(bm, e)) l = penalise(l, ctl->pen);
-        v = __fmul_rn(l, ctl->inv_temp);
-        pass = v >= *reinterpret_cast<const volatile float*>(&ctl->thr);
-    }
-    const uint32_t m = __ballot_sync(0xffffffffu, pass);
-    if (m) {
-        int base = 0;
-        if (lane == 0) base = atomicAdd(&ctl->cnt, __popc(m));
-        base = __shfl_sync(0xffffffffu, base, 0);
-        const int slot = base + __popc(m & ((1u << lane) - 1u));
-        if (pass && slot < S::CAP) {
-            Cand c;
-            c.key = f2key(v);
-            c.idx = (uint32_t)(e + ctl->voff);
-            buf[slot] = c;
-            const float2 bs = *reinterpret_cast<const float2*>(&ctl->hbase);
-            atomicAdd(&hist[hist_bin(v, bs.x, bs.y)], 1u);
+        const uint32_t m = __ballot_sync(0xffffffffu, pass);
+        if (m) {
+            int base = 0;
+            if (lane == 0) base = atomicAdd(&ctl->cnt, __popc(m));
+            base = __shfl_sync(0xffffffffu, base, 0);
+            const int slot = base + __popc(m & ((1u << lane) - 1u));
+            if (pass && slot < S::CAP) {
+                Cand c;
+                c.key = f2key(v);
+                c.idx = (uint32_t)(e + ctl->voff);
+                buf[slot] = c;
+                const float2 bs = *reinterpret_cast<const float2*>(&ctl->hbase);
+                atomicAdd(&hist[hist_bin(v, bs.x, bs.y)], 1u);
+            }
         }
     }
     __syncwarp();

@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
             // warp split over two of its own meeting points does not return)
             __syncwarp();
             const int staged = __shfl_sync(0xffffffffu, wcnt[warp], 0);
-            if (staged >= 24 || (r & (r - 1)) == 0) flush_staged<S, POST>();
+            if (staged >= S::STG * 3 / 4 || (r & (r - 1)) == 0) flush_staged<S, POST>();
             if ((r & (NWARP - 1)) == warp) {
                 const int n = live_count(ctl);
                 const int fresh_entries = __shfl_sync(0xffffffffu, n - ctl->walked, 0);
@@ -345,10 +345,13 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
             __syncthreads();
             thr = t0;
             if (POST) rthr = post_raw_bound(thr, c.inv_temp, POSTP);
+            // (the seed admits a few entries more than k: for long shortlists, more than the staging area
+            // holds, so it is emptied after every vector)
 #pragma unroll
-            for (int u = 0; u < U; u++)
+            for (int u = 0; u < U; u++) {
                 if (v0 + u * NT < b0) filter_vec<S, T, POST>(ra[u], v0 + u * NT, c.mis, c.inv_temp, thr, rthr);
-            flush_staged<S, POST>();
+                if (k >= 128 || u == U - 1) flush_staged<S, POST>();
+            }
         }
         // the first meeting: every append of region 0 is counted before the threshold is read; every
         // warp walks the histogram for itself
