@@ -298,7 +298,7 @@ template <typename T>
 int launch_wide_as(const KArgs& a, cudaStream_t stream) {
     static std::atomic<int> granted[2][kMaxDevices];
     const size_t bitmap = bitmap_words(a.vocab) * sizeof(uint32_t);
-    const size_t smem_hist = WF_CTL_BYTES + 2 * (size_t)WF_BINS * (8 + 4) + (size_t)WF_CAND * 8 + bitmap;
+    const size_t smem_hist = WF_CTL_BYTES + 2 * (size_t)WF_BINS * (8 + 4) + (size_t)WF_BINS * 4 + (size_t)WF_CAND * 8 + bitmap;
     const size_t smem_rows = ((sizeof(WideCtl) + 127) / 128) * 128 + bitmap;
     int rc = ensure_smem(wide_hist_kernel<T>, smem_hist, granted[0]);
     if (rc) return rc;

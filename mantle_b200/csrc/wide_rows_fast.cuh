@@ -156,12 +156,13 @@ template <typename T>
 __global__ void __launch_bounds__(WF_NT, 2) wide_hist_kernel(const KArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     WFCtl* w = reinterpret_cast<WFCtl*>(smem_raw);
-    // [ctl][row histogram words][bin histogram words][row scl][bin scl][entries][bitmap]
+    // [ctl][row histogram words][bin histogram words][row scl][bin scl][counts of the histogram being built][entries][bitmap]
     unsigned long long* words0 = reinterpret_cast<unsigned long long*>(smem_raw + WF_CTL_BYTES);
     unsigned long long* words1 = words0 + WF_BINS;
     float* scl0 = reinterpret_cast<float*>(words1 + WF_BINS);
     float* scl1 = scl0 + WF_BINS;
-    unsigned long long* cand = reinterpret_cast<unsigned long long*>(scl1 + WF_BINS);  // (key << 32 | ~column)
+    uint32_t* cnt32 = reinterpret_cast<uint32_t*>(scl1 + WF_BINS);
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(cnt32 + WF_BINS);  // (key << 32 | ~column)
     uint32_t* bm = reinterpret_cast<uint32_t*>(cand + WF_CAND);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row = blockIdx.x;
@@ -283,6 +284,32 @@ __global__ void __launch_bounds__(WF_NT, 2) wide_hist_kernel(const KArgs a) {
             E = max(E - 1, -100);
             h.scl[b] = __uint_as_float((uint32_t)(24 - E + 127) << 23);  // 2^(24 - E)
             h.words[b] = 0ull;
+            cnt32[b] = 0u;
+        }
+        __syncthreads();
+    };
+    // While a histogram is built its word holds two 32-bit sums -- the low twelve bits of the scaled
+    // weights and the rest -- and the counts sit apart: three 32-bit atomics per entry, which the
+    // shared-memory unit serves several times faster than one 64-bit one.  `pack` (every thread, ends with
+    // a barrier) then puts count << 43 | sum into the word.  A bin of more than 2^18 entries could
+    // overflow a partial sum: its count is packed as 0, which the totals' check turns into "not settled".
+    auto hist_add = [&](const WFHist& h, int b, float ex) {
+        const uint32_t x = __float2uint_rz(__fmul_rn(ex, h.scl[b]));
+        uint32_t* halves = reinterpret_cast<uint32_t*>(&h.words[b]);
+        if (x) {  // a pass that only counts, or a weight of exactly 0
+            atomicAdd(&halves[0], x & 0xfffu);
+            atomicAdd(&halves[1], x >> 12);
+        }
+        atomicAdd(&cnt32[b], 1u);
+    };
+    auto pack = [&](const WFHist& h) {
+        __syncthreads();
+        for (int b = tid; b < WF_BINS; b += WF_NT) {
+            const uint32_t* halves = reinterpret_cast<const uint32_t*>(&h.words[b]);
+            const unsigned long long sum = ((unsigned long long)halves[1] << 12) + halves[0];
+            const uint32_t c = cnt32[b] <= (1u << 18) ? cnt32[b] : 0u;
+            h.words[b] = ((unsigned long long)c << WF_COUNT_SHIFT) | sum;
+            cnt32[b] = 0u;
         }
         __syncthreads();
     };
@@ -347,12 +374,13 @@ __global__ void __launch_bounds__(WF_NT, 2) wide_hist_kernel(const KArgs a) {
                 }
                 if (d <= top.hi) {
                     const int b = bin_of(top, d);
-                    atomicAdd(&top.words[b], (1ull << WF_COUNT_SHIFT) | __float2ull_rz(__fmul_rn(ex, top.scl[b])));
+                    hist_add(top, b, ex);
                     nc++;
                 } else {
                     fc++;
                 }
             });
+            pack(top);
             // totals: counts over threads (the check on the packed words), sums over the bins
             unsigned long long tc = nc, tf = fc;
 #pragma unroll
@@ -622,7 +650,7 @@ __global__ void __launch_bounds__(WF_NT, 2) wide_hist_kernel(const KArgs a) {
                 }
                 if (!collect) {
                     const int b = bin_of(sub, d);
-                    atomicAdd(&sub.words[b], (1ull << WF_COUNT_SHIFT) | __float2ull_rz(__fmul_rn(ex, sub.scl[b])));
+                    hist_add(sub, b, ex);
                     return;
                 }
                 if (at_level == 1) {
@@ -633,7 +661,10 @@ __global__ void __launch_bounds__(WF_NT, 2) wide_hist_kernel(const KArgs a) {
                 if (slot < WF_CAND) cand[slot] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)e);
             });
             __syncthreads();
-            if (!collect) continue;  // locate again, on the bins' own histogram
+            if (!collect) {
+                pack(sub);
+                continue;  // locate again, on the bins' own histogram
+            }
 
             // -- the entries are in shared memory: order them and walk --
             const int n = w->cand_cnt;
