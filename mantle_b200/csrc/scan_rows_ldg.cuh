@@ -170,7 +170,9 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_ldg_kernel(const KAr
     const int a0 = g.a0, b0 = g.b0, elo = g.elo, ehi = g.ehi;
     constexpr int RV = NT * U;  // vectors per region
     const int nreg = g.nchunks;
-    bool careful = k > 32 * NWARP;
+    // (a shape whose longest shortlist the thread maxima can seed never starts on the careful path: its first
+    // loads then do not wait for the row's parameters)
+    bool careful = S::KCAP > 32 * NWARP && k > 32 * NWARP;
 
     // The first region's loads go out before anything else: they are in flight while the bitmap is built.
     uint4 ra[U], rb[U];
