@@ -178,7 +178,6 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
 #pragma unroll
                 for (int u = 0; u < U; u++) one_vector(src[u], VP::finish(part[u], src[u]), v0 + u * NT);
             }
-
         };
         // The item's last region: vectors beyond the end are skipped.
         auto last_region = [&](const uint4(&src)[U], int r) {
@@ -190,7 +189,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
         // After region r one warp (they take turns) walks the histogram, if enough entries have come
         // since the last walk, and raises the threshold; nobody waits for it.  The CTA meets only after
         // regions 1, 2, 4, 8, ...: between two such meetings about k entries arrive however long the
-        // row is, and a meeting that finds the buffer more than half full compacts it.
+        // row is, and a meeting that finds more than FORCE entries in the buffer compacts it.
         auto region_end = [&](int r) {
             // staged survivors are worked off once the area is three quarters full, and before the CTA meets
             // (the count is taken by one lane after the warp has come together again: lanes that read it
