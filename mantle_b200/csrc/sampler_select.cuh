@@ -320,12 +320,13 @@ __device__ __forceinline__ bool hist_compact(Cand* buf, Ctl* ctl, uint32_t* hist
 // Orders the n entries of the buffer (key descending, index ascending) and keeps the best k, for a
 // buffer too long for the counting select: the entries are dealt into HBINS buckets of their value
 // (laid over the buffer's own range), bucket by bucket into the upper half of the buffer, and every
-// thread then orders one bucket by insertion.  n * (a bucket's length) compares in all, four
-// barriers; the radix select followed by the bitonic sort it replaces has sixty.  Returns false, with
+// entry then counts the entries of its own bucket that precede it -- the counting select, bucket by
+// bucket.  n * (a bucket's length) compares in all, four barriers; the radix select followed by the
+// bitonic sort it replaces has sixty.  Returns false, with
 // the buffer as it was, when that does not work out (more than half the buffer in use, a bucket of
 // more than BUCKET_MAX entries: ties, or one value far from the rest); the caller then takes the
 // other way.  Every thread; the buffer quiescent.
-constexpr int BUCKET_MAX = 48;
+constexpr int BUCKET_MAX = 256;
 template <class S>
 __device__ __noinline__ bool bucket_order(int k, int tid) {
     static_assert(S::NT == HBINS, "one bucket per thread");
@@ -411,22 +412,21 @@ __device__ __noinline__ bool bucket_order(int k, int tid) {
         if (i < n) dst[off[place[j] >> 16] + (place[j] & 0xffffu)] = buf[i];
     }
     __syncthreads();
-    {   // one bucket per thread, by insertion
-        const int m = (int)cnt[tid];
-        Cand* seg = dst + off[tid];
-        for (int a = 1; a < m; a++) {
-            const Cand x = seg[a];
-            int c = a - 1;
-            while (c >= 0 && cand_before(x, seg[c])) {
-                seg[c + 1] = seg[c];
-                c--;
-            }
-            seg[c + 1] = x;
+    // every entry counts the entries of its own bucket that precede it and goes to its place in the order;
+    // only the best k places exist
+    const int m = min(n, k);
+#pragma unroll
+    for (int j = 0; j < EPT; j++) {
+        const int i = tid + j * NT;
+        if (i < n) {
+            const uint32_t b = place[j] >> 16;
+            const int first = (int)off[b], len = (int)cnt[b];
+            const Cand me = dst[first + (int)(place[j] & 0xffffu)];
+            int rank = 0;
+            for (int t = 0; t < len; t++) rank += cand_before(dst[first + t], me) ? 1 : 0;
+            if (first + rank < m) buf[first + rank] = me;
         }
     }
-    __syncthreads();
-    const int m = min(n, k);
-    for (int i = tid; i < m; i += NT) buf[i] = dst[i];
     if (tid == 0) ctl->cnt = m;
     __syncthreads();
     return true;

@@ -453,7 +453,7 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
     if constexpr (SEED_HIST) {
         // long shortlists: the buckets order what the counting select cannot take
         __syncthreads();
-        if (!careful && live_count(ctl) > 2 * RANK_MAX) ordered = bucket_order<S>(k, tid);
+        if (!careful && live_count(ctl) > RANK_MAX) ordered = bucket_order<S>(k, tid);
     }
     if (!ordered) refresh_topk<S, true>(buf, ctl, hist, k, tid, &have, &ordered);
     __syncthreads();
