@@ -450,10 +450,11 @@ __global__ void __launch_bounds__(S::NT, S::MINB) scan_rows_hist_kernel(const KA
     }
 
     bool have, ordered = false;
-    if constexpr (SEED_HIST) {
-        // long shortlists: the buckets order what the counting select cannot take
+    {
+        // what is too long for a cheap counting select (from 129 entries on; the larger shape: 257) is
+        // ordered by buckets of its value
         __syncthreads();
-        if (!careful && live_count(ctl) > RANK_MAX) ordered = bucket_order<S>(k, tid);
+        if (!careful && live_count(ctl) > (SEED_HIST ? RANK_MAX : RANK_MAX / 2)) ordered = bucket_order<S>(k, tid);
     }
     if (!ordered) refresh_topk<S, true>(buf, ctl, hist, k, tid, &have, &ordered);
     __syncthreads();
