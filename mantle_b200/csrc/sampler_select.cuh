@@ -304,11 +304,27 @@ __device__ __forceinline__ bool hist_compact(Cand* buf, Ctl* ctl, uint32_t* hist
     __syncthreads();
     if (tid == 0) ctl->cnt = 0;
     __syncthreads();
+    if constexpr (S::KCAP > RANK_MAX) {
+        // long shortlists keep a thousand entries: one reservation per warp and round instead of one per entry
+        const int lane = tid & 31;
 #pragma unroll
-    for (int j = 0; j < EPT; j++) {
-        if ((keep >> j) & 1u) {
-            const int slot = atomicAdd(&ctl->cnt, 1);
-            buf[slot] = mine[j];
+        for (int j = 0; j < EPT; j++) {
+            const bool kj = (keep >> j) & 1u;
+            const uint32_t b = __ballot_sync(0xffffffffu, kj);
+            if (b) {
+                int base = 0;
+                if (lane == 0) base = atomicAdd(&ctl->cnt, __popc(b));
+                base = __shfl_sync(0xffffffffu, base, 0);
+                if (kj) buf[base + __popc(b & ((1u << lane) - 1u))] = mine[j];
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < EPT; j++) {
+            if ((keep >> j) & 1u) {
+                const int slot = atomicAdd(&ctl->cnt, 1);
+                buf[slot] = mine[j];
+            }
         }
     }
     __syncthreads();
