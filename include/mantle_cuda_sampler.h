@@ -31,7 +31,10 @@
  *
  * NaN logits are outside the contract (the reference's own result depends on where in the row
  * they sit).  Here a NaN is never admitted to a shortlist; a row with no other value returns
- * token 0 and raises MANTLE_SAMPLE_STATUS_NAN.
+ * token 0 and raises MANTLE_SAMPLE_STATUS_NAN.  So is a row whose shortlist holds nothing but
+ * -inf (a fully masked row) or whose largest value is +inf: the reference's softmax shifts by the
+ * maximum, inf - inf is NaN, and every probability with it.  Such a row returns one of its shortlist's
+ * ids, or -1 with MANTLE_SAMPLE_STATUS_EMPTY when min_p is set (no probability reaches a NaN threshold).
  *
  * The library keeps a little per-device state (device attributes, kernel attributes, the
  * address of the static scratch): it must not be used across a cudaDeviceReset.
