@@ -46,15 +46,16 @@ def make_logits(rng, rows, V, stop, t, stop_rows):
     return lg
 
 
-@pytest.mark.parametrize("capacity", [64, 512])
-def test_decode_loop_through_the_batch_sampler(capacity):
-    rng = np.random.default_rng(2024 + capacity)
-    rows, V, steps, last_n = 24, 3001, 90, 24
-    stop = [1500, 2500]
+@pytest.mark.parametrize("capacity,V,ks", [(64, 3001, (1, 8, 40)), (512, 3001, (1, 8, 40)),
+                                           (64, 60001, (1, 40, 100))])  # the last: whole rows of the histogram kernel
+def test_decode_loop_through_the_batch_sampler(capacity, V, ks):
+    rng = np.random.default_rng(2024 + capacity + V)
+    rows, steps, last_n = (24 if V < 10000 else 12), 90, 24
+    stop = [1500, V - 501]
     cfgs, reqs = [], []
     for r in range(rows):
         cfg = sampler.SamplerConfig(seed=100 + r, temperature=float(rng.choice([0.0, 0.7, 1.0])),
-                                    top_k=int(rng.choice([1, 8, 40])), top_p=float(rng.choice([0.9, 1.0])),
+                                    top_k=int(rng.choice(ks)), top_p=float(rng.choice([0.9, 1.0])),
                                     repeat_penalty=float(rng.choice([1.0, 1.2, 1.5])), repeat_last_n=last_n)
         prompt = rng.integers(0, V, size=int(rng.integers(0, 20))).tolist()
         cfgs.append(cfg)
