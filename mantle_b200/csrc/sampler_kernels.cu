@@ -247,7 +247,15 @@ int launch_scan_shape(const KArgs& a, int dtype, cudaStream_t stream) {
 // every shortlist length (top_k 20: 0.492 against 0.544 ms).  (Short items -- split rows, narrow vocabulary
 // shards -- used to take the cut kernel at any length; measured again with the histogram kernel as it is now,
 // 1024 rows of 32 768 columns at top_k 50 take 60 against 78 us, 64 rows of 16 882 at top_k 200 31 against 38.)
-bool cut_kernel(const KArgs& a, int) { return a.max_top_k <= CUT_KMAX && a.post.mode == 0; }
+// Items of about one region (a single row split over the whole GPU) are over before the histogram has paid for
+// its set-up: they keep the exact cuts at every shortlist length the small shape serves (one row at top_k 40: 19.1
+// against 20.8 us; from two regions per item on the histogram kernel is ahead: 16 mixed rows 45.3 against 47.2 us).
+bool cut_kernel(const KArgs& a, int dtype) {
+    if (a.post.mode != 0) return false;
+    if (a.max_top_k <= CUT_KMAX) return true;
+    const int per_region = ShapeK256::NT * ShapeK256::U * (dtype == MANTLE_DTYPE_F32 ? 4 : 8);
+    return a.max_top_k <= ShapeK256::KCAP && a.vocab / a.splits <= per_region * 3 / 2;
+}
 
 template <int MODE>
 int launch_scan(const KArgs& a, int dtype, cudaStream_t stream) {
